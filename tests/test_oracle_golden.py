@@ -1,0 +1,53 @@
+"""Pins the CPU oracle against the reference's own golden outputs (the CHECK
+lines of its integration tests).  CPU only."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests import golden_runner
+
+_G = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "comet_golden.json")))
+
+
+@pytest.mark.parametrize("name", sorted(_G["cases"]))
+def test_oracle_matches_reference_check_lines(name, golden, mtx_dir):
+    case = golden["cases"][name]
+    got = golden_runner.run_case(case, mtx_dir, oracle)
+    assert golden_runner.normalise(got) == golden_runner.expected_text(case)
+
+
+def test_triangle_count_two_ways(golden, mtx_dir):
+    """SUM((L*L) .* L) by materialising the masked product equals the direct count."""
+    L = oracle.read_mtx(str(mtx_dir / "tc.mtx"), "CSR", 2)
+    C = oracle.spgemm(L, L, L, oracle.PLUS_PAIR)
+    assert oracle.reduce_sum(C.val) == 5.0
+    assert oracle.masked_pair_count(L, L, L) == 5
+    # unmasked product followed by the elementwise multiply (the first spelling)
+    P = oracle.spgemm(L, L, None, oracle.PLUS_TIMES)
+    E = oracle.elews_csr_csr(P, L)
+    assert oracle.reduce_sum(E.val) == 5.0
+
+
+def test_oracle_against_scipy_random():
+    sp = pytest.importorskip("scipy.sparse")
+    rng = np.random.default_rng(1)
+    A = sp.random(200, 150, density=0.05, random_state=rng, format="csr", dtype=np.float64)
+    B = sp.random(150, 180, density=0.05, random_state=rng, format="csr", dtype=np.float64)
+    A.sort_indices(); B.sort_indices()
+    oa, ob = oracle.from_scipy_csr(A), oracle.from_scipy_csr(B)
+    C = oracle.spgemm(oa, ob)
+    ref = (A @ B).tocsr(); ref.sort_indices()
+    # scipy prunes nothing here either (no explicit zeros arise from random data)
+    assert np.array_equal(C.a2pos, ref.indptr)
+    assert np.array_equal(C.a2crd, ref.indices)
+    np.testing.assert_allclose(C.val, ref.data, rtol=1e-13)
+    x = rng.uniform(-1, 1, 150)
+    np.testing.assert_allclose(oracle.spmv(oa, x), A @ x, rtol=1e-12, atol=1e-14)
+    D = rng.uniform(-1, 1, (150, 7))
+    np.testing.assert_allclose(oracle.spmm(oa, D), A @ D, rtol=1e-12, atol=1e-14)
+    X = rng.uniform(-1, 1, (200, 9)); Y = rng.uniform(-1, 1, (150, 9))
+    want = np.asarray(A.multiply(X @ Y.T).tocsr()[A.nonzero()]).ravel()
+    np.testing.assert_allclose(oracle.sddmm(oa, X, Y), want, rtol=1e-12, atol=1e-14)
