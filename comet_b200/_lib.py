@@ -1,0 +1,91 @@
+"""Loads ``libcomet_b200.so`` (built in-tree by ``comet_b200.build``) and declares
+the C ABI of ``include/comet_b200.h`` for ctypes.  There is no fallback: if the
+library is missing or fails to load, importing an operation raises."""
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_double, c_int32, c_int64, c_void_p
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcomet_b200.so")
+
+
+class MemRef1D(Structure):
+    """StridedMemRefType<T,1>; same field order as cometpy's memref_i64/f64
+    (frontends/numpy-scipy/cometpy/MLIRGen/utils.py:5-21)."""
+    _fields_ = [("allocated", c_void_p), ("aligned", c_void_p), ("offset", c_int64),
+                ("sizes", c_int64 * 1), ("strides", c_int64 * 1)]
+
+
+class MemRef2D(Structure):
+    _fields_ = [("allocated", c_void_p), ("aligned", c_void_p), ("offset", c_int64),
+                ("sizes", c_int64 * 2), ("strides", c_int64 * 2)]
+
+
+_SPARSE = [c_int32] * 4 + [c_int64, c_void_p] * 10          # formats, 8 index arrays, vals, dims
+_MEMREF = [c_int64, c_void_p]
+
+SIGNATURES = {
+    # layer 1: host memref descriptors
+    "comet_b200_spmv_f64_i64": (None, _SPARSE + _MEMREF * 2 + [c_int32, c_int32]),
+    "comet_b200_spmm_f64_i64": (None, _SPARSE + _MEMREF * 2 + [c_int32, c_int32]),
+    "comet_b200_sddmm_f64_i64": (None, _SPARSE + _MEMREF * 2 + _SPARSE),
+    "comet_b200_elews_mul_sparse_dense_f64_i64": (None, _SPARSE + _MEMREF + _SPARSE),
+    "comet_b200_spgemm_symbolic_f64_i64": (c_int64, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF * 2),
+    "comet_b200_spgemm_numeric_f64_i64": (None, [c_int64] + _MEMREF * 2),
+    "comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64": (c_int64, _SPARSE * 2 + _MEMREF * 2),
+    "comet_b200_handle_destroy": (None, [c_int64]),
+    "comet_b200_masked_spgemm_count_f64_i64": (None, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF),
+    "comet_b200_last_error": (ctypes.c_char_p, []),
+    "comet_b200_set_error_mode": (None, [c_int32]),
+    "comet_b200_version": (c_int32, []),
+    "comet_b200_release_scratch": (None, []),
+    # layer 2: device pointers
+    "comet_b200_dev_spmv_f64_i64": (c_int32, [c_int64, c_int64] + [c_void_p] * 6 + [c_int32, c_int32, c_void_p]),
+    "comet_b200_dev_spmm_f64_i64": (c_int32, [c_int64] * 4 + [c_void_p] * 5 + [c_int64, c_void_p, c_int64,
+                                              c_int32, c_int32, c_int32, c_void_p]),
+    "comet_b200_dev_sddmm_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 4 + [c_int64, c_void_p, c_int64,
+                                               c_void_p, c_void_p]),
+    "comet_b200_dev_transpose_f64": (c_int32, [c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "comet_b200_dev_elews_mul_sparse_dense_f64_i64": (c_int32, [c_int64, c_int64] + [c_void_p] * 5 +
+                                                      [c_int64, c_void_p, c_void_p]),
+    "comet_b200_dev_spgemm_symbolic_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 8 + [c_int32, c_void_p,
+                                                         POINTER(c_int64), POINTER(c_int64), c_void_p]),
+    "comet_b200_dev_elews_mul_sparse_sparse_symbolic_f64_i64": (c_int32, [c_int64] + [c_void_p] * 7 +
+                                                                [POINTER(c_int64), POINTER(c_int64), c_void_p]),
+    "comet_b200_dev_spgemm_numeric_f64_i64": (c_int32, [c_int64, c_void_p, c_void_p, c_int32, c_void_p]),
+    "comet_b200_dev_masked_spgemm_count_f64_i64": (c_int32, [c_int64] * 6 + [c_void_p] * 7 + [c_void_p]),
+}
+
+_lib = None
+
+
+class CometB200Error(RuntimeError):
+    pass
+
+
+def load():
+    """Returns the loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise CometB200Error(
+                "libcomet_b200.so is missing (%s). Build it with `python -m comet_b200.build`; "
+                "there is no CPU fallback." % LIB_PATH)
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        # Python callers want exceptions, not exit(1)
+        lib.comet_b200_set_error_mode(1)
+        _lib = lib
+    return _lib
+
+
+def check(status=0):
+    """Raises if the last call reported an error."""
+    msg = load().comet_b200_last_error()
+    if msg:
+        raise CometB200Error(msg.decode())
+    if status:
+        raise CometB200Error("libcomet_b200 call failed with status %d" % status)

@@ -1,0 +1,276 @@
+"""Host-side mirror of the operations COMET's front ends reach the sparse hot
+path with, executed through the C ABI of ``libcomet_b200`` (layer 1: host
+memref descriptors, the same calls a COMET lowering would emit).
+
+Operands are packed the way cometpy packs them for ``_mlir_ciface_`` calls
+(frontends/numpy-scipy/cometpy/MLIRGen/lowering.py:283-360): a dims array, then
+per dimension pos / crd arrays, then values; index arrays are int64 and values
+float64.  Sparse operands may be
+
+  * any object with ``format`` ('CSR' | 'DCSR' | 'COO'), ``nrows``, ``ncols`` and
+    the COMET arrays ``a1pos, a1crd, a2pos, a2crd, val`` (what COMET's reader
+    produces, lib/ExecutionEngine/SparseUtils.cpp:1643-1751), or
+  * a scipy.sparse CSR / COO matrix (what cometpy accepts, CSC rejected).
+
+Function names follow the cometpy surface: ``A @ x`` -> spmv/spmm,
+``A.multiply(B)`` -> elews_mul, ``einsum('ij,jk->ik', A, B, mask=M,
+mask_type='push', semiring='+,pair')`` -> spgemm
+(frontends/numpy-scipy/cometpy/comet.py:1014-1088, 1210-1319).
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from ._lib import MemRef1D, MemRef2D
+
+PLUS_TIMES = 0
+PLUS_PAIR = 1
+MASK_NONE = 0
+MASK_PUSH = 1
+
+_FMT = {"CSR": (0, 1), "DCSR": (1, 1), "COO": (2, 3)}
+_SEMIRINGS = {"+,*": PLUS_TIMES, "plusxy_times": PLUS_TIMES, "+,pair": PLUS_PAIR,
+              "plusxy_pairxy": PLUS_PAIR, PLUS_TIMES: PLUS_TIMES, PLUS_PAIR: PLUS_PAIR}
+
+
+class SparseTensor:
+    """COMET's per-dimension arrays for one sparse matrix (int64 / float64)."""
+
+    def __init__(self, fmt, nrows, ncols, a1pos, a1crd, a2pos, a2crd, val):
+        self.format = fmt
+        self.nrows, self.ncols = int(nrows), int(ncols)
+        self.a1pos, self.a1crd, self.a2pos, self.a2crd, self.val = a1pos, a1crd, a2pos, a2crd, val
+
+    @property
+    def nnz(self):
+        return int(self.val.shape[0])
+
+    @property
+    def shape(self):
+        return (self.nrows, self.ncols)
+
+    def to_scipy(self):
+        import scipy.sparse as sp
+        if self.format == "CSR":
+            return sp.csr_matrix((self.val, self.a2crd, self.a2pos), shape=self.shape)
+        if self.format == "COO":
+            return sp.coo_matrix((self.val, (self.a1crd, self.a2crd)), shape=self.shape)
+        raise ValueError("to_scipy: unsupported format " + self.format)
+
+
+def _i64(a):
+    return np.ascontiguousarray(a, dtype=np.int64)
+
+
+def _f64(a):
+    return np.ascontiguousarray(a, dtype=np.float64)
+
+
+def as_sparse(m):
+    """scipy CSR/COO or a COMET-array object -> SparseTensor with int64/float64 arrays."""
+    if isinstance(m, SparseTensor):
+        return m
+    if hasattr(m, "a2crd") and hasattr(m, "format") and isinstance(m.format, str) and m.format.isupper():
+        return SparseTensor(m.format, m.nrows, m.ncols, _i64(m.a1pos), _i64(m.a1crd), _i64(m.a2pos),
+                            _i64(m.a2crd), _f64(m.val))
+    fmt = getattr(m, "format", None)
+    if fmt == "csr":
+        return SparseTensor("CSR", m.shape[0], m.shape[1], np.array([m.shape[0]], dtype=np.int64),
+                            np.array([-1], dtype=np.int64), _i64(m.indptr), _i64(m.indices), _f64(m.data))
+    if fmt == "coo":
+        return SparseTensor("COO", m.shape[0], m.shape[1], np.array([0, m.nnz], dtype=np.int64),
+                            _i64(m.row), np.array([-1], dtype=np.int64), _i64(m.col), _f64(m.data))
+    raise TypeError("unsupported sparse operand: %r (CSR and COO are accepted, like cometpy)" % type(m))
+
+
+class _Packer:
+    """Builds the (rank, descriptor*) argument pairs and keeps the arrays alive."""
+
+    def __init__(self):
+        self.keep = []
+
+    def m1(self, arr):
+        arr = np.ascontiguousarray(arr)
+        d = MemRef1D()
+        d.allocated = d.aligned = arr.ctypes.data
+        d.offset = 0
+        d.sizes[0] = arr.shape[0]
+        d.strides[0] = 1
+        self.keep += [arr, d]
+        return [1, ctypes.addressof(d)]
+
+    def m2(self, arr, transposed_view=False):
+        d = MemRef2D()
+        d.allocated = d.aligned = arr.ctypes.data
+        d.offset = 0
+        if transposed_view:       # present row-major [n, k] as a {k, n} memref with strides {1, ld}
+            d.sizes[0], d.sizes[1] = arr.shape[1], arr.shape[0]
+            d.strides[0], d.strides[1] = 1, arr.strides[0] // arr.itemsize
+        else:
+            d.sizes[0], d.sizes[1] = arr.shape
+            d.strides[0], d.strides[1] = arr.strides[0] // arr.itemsize, arr.strides[1] // arr.itemsize
+        self.keep += [arr, d]
+        return [2, ctypes.addressof(d)]
+
+    def sparse(self, t):
+        f1, f2 = _FMT[t.format]
+        empty = np.zeros(0, dtype=np.int64)
+        dims = np.array([t.nrows, t.ncols], dtype=np.int64)
+        args = [f1, -1, f2, -1]
+        args += self.m1(t.a1pos) + self.m1(t.a1crd) + self.m1(empty) + self.m1(empty)
+        args += self.m1(t.a2pos) + self.m1(t.a2crd) + self.m1(empty) + self.m1(empty)
+        args += self.m1(t.val) + self.m1(dims)
+        return args
+
+
+def _semiring(s):
+    if s is None:
+        return PLUS_TIMES
+    key = s.replace(" ", "") if isinstance(s, str) else s
+    if key not in _SEMIRINGS:
+        raise ValueError("unsupported semiring %r (plus-times and plus-pair are handled)" % (s,))
+    return _SEMIRINGS[key]
+
+
+def spmv(A, x, y0=None, semiring=PLUS_TIMES):
+    """y = y0 + A @ x  (ta.mul, sparse x dense vector)."""
+    A = as_sparse(A)
+    lib = _lib.load()
+    pk = _Packer()
+    x = _f64(x)
+    y = np.zeros(A.nrows) if y0 is None else _f64(y0).copy()
+    lib.comet_b200_spmv_f64_i64(*pk.sparse(A), *pk.m1(x), *pk.m1(y), _semiring(semiring),
+                                0 if y0 is None else 1)
+    _lib.check()
+    return y
+
+
+def spmm(A, B, C0=None, semiring=PLUS_TIMES):
+    """C = C0 + A @ B  (ta.mul, sparse x dense matrix), B row-major."""
+    A = as_sparse(A)
+    lib = _lib.load()
+    pk = _Packer()
+    B = _f64(B)
+    C = np.zeros((A.nrows, B.shape[1])) if C0 is None else _f64(C0).copy()
+    lib.comet_b200_spmm_f64_i64(*pk.sparse(A), *pk.m2(B), *pk.m2(C), _semiring(semiring),
+                                0 if C0 is None else 1)
+    _lib.check()
+    return C
+
+
+def sddmm(S, X, Y, y_is_kj=False):
+    """values of S .* (X @ Y^T) on S's pattern.  Y is [cols, K] row-major, or the
+    [K, cols] operand D[k,j] of the reference's sddmm.ta when ``y_is_kj``."""
+    S = as_sparse(S)
+    lib = _lib.load()
+    pk = _Packer()
+    X, Y = _f64(X), _f64(Y)
+    out = SparseTensor("CSR", S.nrows, S.ncols, np.zeros_like(S.a1pos), np.zeros_like(S.a1crd),
+                       np.zeros_like(S.a2pos), np.zeros_like(S.a2crd), np.zeros(S.nnz))
+    d_args = pk.m2(Y) if y_is_kj else pk.m2(Y, transposed_view=True)
+    lib.comet_b200_sddmm_f64_i64(*pk.sparse(S), *pk.m2(X), *d_args, *pk.sparse(out))
+    _lib.check()
+    assert np.array_equal(out.a2pos, S.a2pos) and np.array_equal(out.a2crd, S.a2crd)
+    return out.val
+
+
+def elews_sparse_dense(A, B):
+    """values of A .* B on A's pattern (A CSR or COO, B dense)."""
+    A = as_sparse(A)
+    lib = _lib.load()
+    pk = _Packer()
+    B = _f64(B)
+    out = SparseTensor(A.format, A.nrows, A.ncols, np.zeros_like(A.a1pos), np.zeros_like(A.a1crd),
+                       np.zeros_like(A.a2pos), np.zeros_like(A.a2crd), np.zeros(A.nnz))
+    lib.comet_b200_elews_mul_sparse_dense_f64_i64(*pk.sparse(A), *pk.m2(B), *pk.sparse(out))
+    _lib.check()
+    return out.val
+
+
+def _finish_sparse_out(lib, handle, nrows, ncols, cpos, sizes):
+    _lib.check()
+    nnz = int(sizes[8])
+    ccrd = np.zeros(nnz, dtype=np.int64)
+    cval = np.zeros(nnz, dtype=np.float64)
+    pk = _Packer()
+    lib.comet_b200_spgemm_numeric_f64_i64(handle, *pk.m1(ccrd), *pk.m1(cval))
+    _lib.check()
+    return SparseTensor("CSR", nrows, ncols, np.array([nrows], dtype=np.int64),
+                        np.array([-1], dtype=np.int64), cpos, ccrd, cval)
+
+
+def spgemm(A, B, M=None, semiring=PLUS_TIMES):
+    """C = A @ B, or C<M,push> = A @ B, all CSR; returns a CSR SparseTensor."""
+    A, B = as_sparse(A), as_sparse(B)
+    Mt = as_sparse(M) if M is not None else A
+    lib = _lib.load()
+    pk = _Packer()
+    cpos = np.zeros(A.nrows + 1, dtype=np.int64)
+    sizes = np.zeros(11, dtype=np.int64)
+    handle = lib.comet_b200_spgemm_symbolic_f64_i64(
+        *pk.sparse(A), *pk.sparse(B), *pk.sparse(Mt), MASK_PUSH if M is not None else MASK_NONE,
+        _semiring(semiring), *pk.m1(cpos), *pk.m1(sizes))
+    return _finish_sparse_out(lib, handle, A.nrows, B.ncols, cpos, sizes)
+
+
+def elews_csr_csr(A, B):
+    """C = A .* B with both operands CSR."""
+    A, B = as_sparse(A), as_sparse(B)
+    lib = _lib.load()
+    pk = _Packer()
+    cpos = np.zeros(A.nrows + 1, dtype=np.int64)
+    sizes = np.zeros(11, dtype=np.int64)
+    handle = lib.comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64(
+        *pk.sparse(A), *pk.sparse(B), *pk.m1(cpos), *pk.m1(sizes))
+    return _finish_sparse_out(lib, handle, A.nrows, A.ncols, cpos, sizes)
+
+
+def masked_pair_count(A, B, M):
+    """SUM(C<M,push> = A @ B) under plus-pair as an exact integer."""
+    A, B, M = as_sparse(A), as_sparse(B), as_sparse(M)
+    lib = _lib.load()
+    pk = _Packer()
+    out = np.zeros(1, dtype=np.int64)
+    lib.comet_b200_masked_spgemm_count_f64_i64(*pk.sparse(A), *pk.sparse(B), *pk.sparse(M), MASK_PUSH,
+                                               PLUS_PAIR, *pk.m1(out))
+    _lib.check()
+    return int(out[0])
+
+
+def triangle_count(L):
+    """Sandia LL: sum((L @ L) .* L) for the strict lower triangle L of a symmetric graph
+    (test/integration/kernels/triangleCount_SandiaLL_wMasking.ta)."""
+    return masked_pair_count(L, L, L)
+
+
+def reduce_sum(vals):
+    """ta.reduce over stored values.  Not part of the device path: the values are
+    host memrefs after every call, and COMET's generated loop sums them there
+    (lib/Conversion/TensorAlgebraToSCF/TensorAlgebraToSCF.cpp:483-517)."""
+    s = 0.0
+    for v in np.asarray(vals, dtype=np.float64).ravel():
+        s = s + float(v)
+    return s
+
+
+def einsum(subscripts, A, B, mask=None, mask_type="push", semiring="+,*"):
+    """The cometpy einsum forms that reach the sparse hot path
+    (frontends/numpy-scipy/cometpy/comet.py:1210-1319): 'ij,jk->ik' with a sparse
+    first operand and a dense or sparse second one, and 'ij,j->i'."""
+    spec = subscripts.replace(" ", "")
+    lhs, out = spec.split("->")
+    a, b = lhs.split(",")
+    if not (len(a) == 2 and a[1] == b[0]):
+        raise ValueError("unsupported einsum " + subscripts)
+    if mask is not None and mask_type != "push":
+        raise ValueError("only the push mask is handled")
+    sr = _semiring(semiring)
+    sparse_b = hasattr(B, "format") or hasattr(B, "a2crd")
+    if len(b) == 1 and out == a[0]:
+        return spmv(A, B, semiring=sr)
+    if len(b) == 2 and out == a[0] + b[1]:
+        if sparse_b:
+            return spgemm(A, B, mask, sr)
+        return spmm(A, B, semiring=sr)
+    raise ValueError("unsupported einsum " + subscripts)

@@ -1,0 +1,573 @@
+// Layer 1 of the C ABI: entry points that take COMET's host memref descriptors.
+// Each one stages its operands into device memory on the library stream, calls
+// the device-pointer entry point, copies the results back into the caller's
+// memrefs and synchronises, so the generated host code that follows (printing,
+// ta.reduce, the next ta.mul) sees finished host arrays, as it does after the
+// loops COMET generates today.
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+
+extern "C" {
+// device-pointer layer (declared in include/comet_b200.h)
+}
+
+namespace cb200 {
+
+struct Arr {   // a 1-D host memref
+    void *data;
+    int64_t n;
+};
+
+static int get1d(const char *what, int64_t rank, void *desc, size_t elem, Arr *out)
+{
+    out->data = nullptr;
+    out->n = 0;
+    if (!desc) return 0;
+    if (rank != 1) return fail("%s: expected a rank-1 memref, got rank %lld", what, (long long)rank);
+    comet_b200_memref1d *m = (comet_b200_memref1d *)desc;
+    if (m->sizes[0] < 0) return fail("%s: negative size", what);
+    if (m->sizes[0] > 1 && m->strides[0] != 1) return fail("%s: stride must be 1", what);
+    out->data = (char *)m->aligned + m->offset * (int64_t)elem;
+    out->n = m->sizes[0];
+    return 0;
+}
+
+struct Mat {   // a 2-D host memref
+    double *data;
+    int64_t rows, cols, s0, s1;
+};
+
+static int get2d(const char *what, int64_t rank, void *desc, Mat *out)
+{
+    if (!desc || rank != 2) return fail("%s: expected a rank-2 memref", what);
+    comet_b200_memref2d *m = (comet_b200_memref2d *)desc;
+    out->data = (double *)m->aligned + m->offset;
+    out->rows = m->sizes[0];
+    out->cols = m->sizes[1];
+    out->s0 = m->strides[0];
+    out->s1 = m->strides[1];
+    if (out->rows < 0 || out->cols < 0) return fail("%s: negative size", what);
+    return 0;
+}
+
+enum { F_CSR, F_DCSR, F_COO };
+
+struct HostSparse {
+    int fmt;
+    int64_t nrows, ncols, nnz, nstored;   // nstored: rows held (DCSR), else nrows
+    int64_t *a1pos, *a1crd, *a2pos, *a2crd;
+    double *val;
+};
+
+#define SPARSE_ARGS(P) P##1format, P##2format, P##1pos_rank, P##1pos_ptr, P##1crd_rank, P##1crd_ptr, \
+    P##2pos_rank, P##2pos_ptr, P##2crd_rank, P##2crd_ptr, P##val_rank, P##val_ptr, P##dims_rank, P##dims_ptr
+
+static int get_sparse(const char *what, int32_t f1, int32_t f2, int64_t r1p, void *p1p, int64_t r1c,
+                      void *p1c, int64_t r2p, void *p2p, int64_t r2c, void *p2c, int64_t rv, void *pv,
+                      int64_t rd, void *pd, HostSparse *s)
+{
+    Arr a1pos, a1crd, a2pos, a2crd, val, dims;
+    CB_TRY(get1d(what, r1p, p1p, 8, &a1pos));
+    CB_TRY(get1d(what, r1c, p1c, 8, &a1crd));
+    CB_TRY(get1d(what, r2p, p2p, 8, &a2pos));
+    CB_TRY(get1d(what, r2c, p2c, 8, &a2crd));
+    CB_TRY(get1d(what, rv, pv, 8, &val));
+    CB_TRY(get1d(what, rd, pd, 8, &dims));
+    if (dims.n < 2 || !dims.data) return fail("%s: dims memref must hold {rows, cols}", what);
+    s->nrows = ((int64_t *)dims.data)[0];
+    s->ncols = ((int64_t *)dims.data)[1];
+    if (s->nrows < 0 || s->ncols < 0) return fail("%s: negative dimension", what);
+    s->a1pos = (int64_t *)a1pos.data; s->a1crd = (int64_t *)a1crd.data;
+    s->a2pos = (int64_t *)a2pos.data; s->a2crd = (int64_t *)a2crd.data;
+    s->val = (double *)val.data;
+    if (f1 == COMET_B200_FMT_DENSE && f2 == COMET_B200_FMT_CU) {
+        s->fmt = F_CSR;
+        if (a2pos.n < s->nrows + 1) return fail("%s: CSR pos array shorter than rows+1", what);
+        s->nstored = s->nrows;
+        s->nnz = s->nrows > 0 ? s->a2pos[s->nrows] : 0;
+    } else if (f1 == COMET_B200_FMT_CU && f2 == COMET_B200_FMT_CU) {
+        s->fmt = F_DCSR;
+        if (a1pos.n < 2) return fail("%s: DCSR A1pos must hold {0, stored rows}", what);
+        s->nstored = s->a1pos[1] - s->a1pos[0];
+        if (s->a1pos[0] != 0) return fail("%s: DCSR A1pos[0] must be 0", what);
+        if (a1crd.n < s->nstored || a2pos.n < s->nstored + 1)
+            return fail("%s: DCSR arrays shorter than the stored row count", what);
+        s->nnz = s->nstored > 0 ? s->a2pos[s->nstored] : 0;
+    } else if (f1 == COMET_B200_FMT_CN && f2 == COMET_B200_FMT_S) {
+        s->fmt = F_COO;
+        if (a1pos.n < 2) return fail("%s: COO A1pos must hold {0, nnz}", what);
+        if (s->a1pos[0] != 0) return fail("%s: COO A1pos[0] must be 0", what);
+        s->nnz = s->a1pos[1];
+        s->nstored = s->nrows;
+        if (a1crd.n < s->nnz) return fail("%s: COO row coordinates shorter than nnz", what);
+    } else {
+        return fail("%s: unsupported format (%d, %d); CSR, DCSR and COO are handled", what, f1, f2);
+    }
+    if (s->nnz < 0) return fail("%s: negative nnz", what);
+    if (a2crd.n < s->nnz || val.n < s->nnz) return fail("%s: crd/val arrays shorter than nnz", what);
+    return 0;
+}
+
+// Device allocations of one call; freed (stream-ordered) when the object dies
+// unless released to a longer-lived owner.
+struct DevBag {
+    cudaStream_t st;
+    std::vector<void *> ptrs;
+    explicit DevBag(cudaStream_t s) : st(s) {}
+    ~DevBag() { for (void *p : ptrs) cudaFreeAsync(p, st); }
+    int alloc(void **p, size_t bytes)
+    {
+        if (bytes == 0) bytes = 8;
+        cudaError_t e = cudaMallocAsync(p, bytes, st);
+        if (e != cudaSuccess) {
+            *p = nullptr;
+            return fail("device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        }
+        ptrs.push_back(*p);
+        return 0;
+    }
+    int upload(void **p, const void *host, size_t bytes)
+    {
+        CB_TRY(alloc(p, bytes));
+        if (bytes) CB_CUDA(cudaMemcpyAsync(*p, host, bytes, cudaMemcpyHostToDevice, st));
+        return 0;
+    }
+};
+
+struct DevSparse {
+    int64_t nrows_k;          // rows the kernels iterate over (stored rows for DCSR)
+    int64_t *row_ids;         // DCSR row coordinates or null
+    int64_t *pos, *crd, *rows;
+    double *val;
+};
+
+static int pool_keep()
+{
+    static bool done[64] = {false};
+    int d = 0;
+    CB_CUDA(cudaGetDevice(&d));
+    if (d >= 0 && d < 64 && !done[d]) {
+        cudaMemPool_t pool;
+        CB_CUDA(cudaDeviceGetDefaultMemPool(&pool, d));
+        uint64_t keep = ~(uint64_t)0;
+        CB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        done[d] = true;
+    }
+    return 0;
+}
+
+// Uploads a sparse operand; for COO it also derives the row pointer on the device.
+static int upload_sparse(const char *what, const HostSparse &h, DevBag &bag, DevSparse *d,
+                         bool need_val = true)
+{
+    memset(d, 0, sizeof(*d));
+    cudaStream_t st = bag.st;
+    CB_TRY(bag.upload((void **)&d->crd, h.a2crd, (size_t)h.nnz * 8));
+    if (need_val) CB_TRY(bag.upload((void **)&d->val, h.val, (size_t)h.nnz * 8));
+    if (h.fmt == F_CSR) {
+        d->nrows_k = h.nrows;
+        CB_TRY(bag.upload((void **)&d->pos, h.a2pos, (size_t)(h.nrows + 1) * 8));
+    } else if (h.fmt == F_DCSR) {
+        d->nrows_k = h.nstored;
+        CB_TRY(bag.upload((void **)&d->pos, h.a2pos, (size_t)(h.nstored + 1) * 8));
+        CB_TRY(bag.upload((void **)&d->row_ids, h.a1crd, (size_t)h.nstored * 8));
+    } else {
+        d->nrows_k = h.nrows;
+        CB_TRY(bag.upload((void **)&d->rows, h.a1crd, (size_t)h.nnz * 8));
+        CB_TRY(bag.alloc((void **)&d->pos, (size_t)(h.nrows + 1) * 8));
+        int *flag = nullptr;
+        CB_TRY(bag.alloc((void **)&flag, sizeof(int)));
+        int one = 1, got = 1;
+        CB_CUDA(cudaMemcpyAsync(flag, &one, sizeof(int), cudaMemcpyHostToDevice, st));
+        CB_TRY(coo_rows_to_pos(d->rows, h.nnz, h.nrows, d->pos, flag, st));
+        CB_CUDA(cudaMemcpyAsync(&got, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+        CB_CUDA(cudaStreamSynchronize(st));
+        if (!got)
+            return fail("%s: COO row coordinates must be ascending and inside [0, rows) "
+                        "(the order the reference reader produces)", what);
+    }
+    return 0;
+}
+
+static int finish(cudaStream_t st)
+{
+    CB_CUDA(cudaStreamSynchronize(st));
+    return 0;
+}
+
+static int need_stream(cudaStream_t *st)
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0)
+        return fail("no CUDA device is available; libcomet_b200 has no CPU path");
+    *st = lib_stream();
+    if (!*st) return fail("could not create the library stream");
+    return pool_keep();
+}
+
+// Handles created through the host layer also own their staged operands.
+struct HostPlan {
+    int64_t dev_handle;
+    std::vector<void *> owned;
+    int64_t nnz;
+};
+static std::mutex g_hp_mu;
+static std::unordered_map<int64_t, HostPlan *> g_hplans;
+
+static void fill_sizes(void *sizes_ptr, int64_t sizes_rank, int64_t nrows, int64_t ncols, int64_t nnz)
+{
+    Arr s;
+    if (get1d("sizes", sizes_rank, sizes_ptr, 8, &s) != 0 || !s.data) return;
+    // layout of read_input_sizes_2D for CSR (lib/ExecutionEngine/SparseUtils.cpp:1672-1687)
+    int64_t v[11] = {1, 1, 0, 0, nrows + 1, nnz, 0, 0, nnz, nrows, ncols};
+    for (int i = 0; i < 11 && i < s.n; i++) ((int64_t *)s.data)[i] = v[i];
+}
+
+static int spmv_host(const HostSparse &A, Arr x, Arr y, int semiring, int accumulate)
+{
+    if (x.n < A.ncols) return fail("spmv: x shorter than the column count");
+    if (y.n < A.nrows) return fail("spmv: y shorter than the row count");
+    cudaStream_t st;
+    CB_TRY(need_stream(&st));
+    DevBag bag(st);
+    DevSparse dA;
+    CB_TRY(upload_sparse("spmv", A, bag, &dA));
+    double *dx, *dy;
+    CB_TRY(bag.upload((void **)&dx, x.data, (size_t)A.ncols * 8));
+    bool keep_old = accumulate || A.fmt == F_DCSR;   // rows DCSR does not store keep their value
+    if (keep_old) CB_TRY(bag.upload((void **)&dy, y.data, (size_t)A.nrows * 8));
+    else CB_TRY(bag.alloc((void **)&dy, (size_t)A.nrows * 8));
+    if (!accumulate && A.fmt == F_DCSR) CB_CUDA(cudaMemsetAsync(dy, 0, (size_t)A.nrows * 8, st));
+    CB_TRY(comet_b200_dev_spmv_f64_i64(dA.nrows_k, A.nnz, dA.row_ids, dA.pos, dA.crd, dA.val, dx, dy,
+                                       semiring, accumulate, st));
+    CB_CUDA(cudaMemcpyAsync(y.data, dy, (size_t)A.nrows * 8, cudaMemcpyDeviceToHost, st));
+    return finish(st);
+}
+
+static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiring, int accumulate)
+{
+    if (B.rows < A.ncols) return fail("spmm: B has fewer rows than A has columns");
+    if (C.rows < A.nrows || C.cols != B.cols) return fail("spmm: C has the wrong shape");
+    if ((B.cols > 1 && B.s1 != 1) || (C.cols > 1 && C.s1 != 1) || B.s0 < B.cols || C.s0 < C.cols)
+        return fail("spmm: B and C must be row-major");
+    cudaStream_t st;
+    CB_TRY(need_stream(&st));
+    DevBag bag(st);
+    DevSparse dA;
+    CB_TRY(upload_sparse("spmm", A, bag, &dA));
+    const int64_t k = B.cols;
+    double *dB, *dC;
+    CB_TRY(bag.upload((void **)&dB, B.data, (size_t)((A.ncols - 1) * B.s0 + k) * 8 * (A.ncols > 0)));
+    size_t cbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * C.s0 + k) * 8 : 0;
+    bool keep_old = accumulate || A.fmt == F_DCSR || C.s0 != k;
+    if (keep_old) CB_TRY(bag.upload((void **)&dC, C.data, cbytes));
+    else CB_TRY(bag.alloc((void **)&dC, cbytes));
+    if (!accumulate && A.fmt == F_DCSR) CB_CUDA(cudaMemsetAsync(dC, 0, cbytes, st));
+    CB_TRY(comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, k, dA.row_ids, dA.pos, dA.crd,
+                                       dA.val, dB, B.s0, dC, C.s0, semiring, accumulate, 0, st));
+    if (cbytes) CB_CUDA(cudaMemcpyAsync(C.data, dC, cbytes, cudaMemcpyDeviceToHost, st));
+    return finish(st);
+}
+
+static void copy_pattern(const HostSparse &src, const HostSparse &dst)
+{
+    // the output tensor shares the sparse operand's pos/crd
+    // (lib/Conversion/IndexTreeToSCF/SymbolicDomainConversion.cpp:277-297)
+    if (src.fmt == F_CSR) {
+        if (dst.a1pos && dst.a1pos != src.a1pos) dst.a1pos[0] = src.nrows;
+        if (dst.a2pos != src.a2pos) memcpy(dst.a2pos, src.a2pos, (size_t)(src.nrows + 1) * 8);
+    } else if (src.fmt == F_COO) {
+        if (dst.a1pos != src.a1pos) { dst.a1pos[0] = 0; dst.a1pos[1] = src.nnz; }
+        if (dst.a1crd != src.a1crd) memcpy(dst.a1crd, src.a1crd, (size_t)src.nnz * 8);
+    }
+    if (dst.a2crd != src.a2crd) memcpy(dst.a2crd, src.a2crd, (size_t)src.nnz * 8);
+}
+
+}  // namespace cb200
+
+using namespace cb200;
+
+#define GET_SPARSE(name, P, hs) \
+    get_sparse(name, P##1format, P##2format, P##1pos_rank, P##1pos_ptr, P##1crd_rank, P##1crd_ptr, \
+               P##2pos_rank, P##2pos_ptr, P##2crd_rank, P##2crd_ptr, P##val_rank, P##val_ptr,       \
+               P##dims_rank, P##dims_ptr, hs)
+
+#define UNUSED_TILES(P) (void)P##1tile_format; (void)P##2tile_format; (void)P##1tile_pos_rank; \
+    (void)P##1tile_pos_ptr; (void)P##1tile_crd_rank; (void)P##1tile_crd_ptr; (void)P##2tile_pos_rank; \
+    (void)P##2tile_pos_ptr; (void)P##2tile_crd_rank; (void)P##2tile_crd_ptr
+
+extern "C" {
+
+void comet_b200_spmv_f64_i64(COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr, int64_t y_rank,
+                             void *y_ptr, int32_t semiring, int32_t accumulate)
+{
+    UNUSED_TILES(A);
+    clear_error();
+    HostSparse A;
+    Arr x, y;
+    if (GET_SPARSE("spmv: A", A, &A)) return;
+    if (get1d("spmv: x", x_rank, x_ptr, 8, &x) || get1d("spmv: y", y_rank, y_ptr, 8, &y)) return;
+    spmv_host(A, x, y, semiring, accumulate);
+}
+
+void comet_b200_spmm_f64_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank,
+                             void *C_ptr, int32_t semiring, int32_t accumulate)
+{
+    UNUSED_TILES(A);
+    clear_error();
+    HostSparse A;
+    Mat B, C;
+    if (GET_SPARSE("spmm: A", A, &A)) return;
+    if (get2d("spmm: B", B_rank, B_ptr, &B) || get2d("spmm: C", C_rank, C_ptr, &C)) return;
+    spmm_host(A, B, C, semiring, accumulate);
+}
+
+void comet_b200_sddmm_f64_i64(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank,
+                              void *D_ptr, COMET_B200_SPARSE2D(O))
+{
+    UNUSED_TILES(S);
+    UNUSED_TILES(O);
+    clear_error();
+    HostSparse S, O;
+    Mat X, D;
+    if (GET_SPARSE("sddmm: S", S, &S) || GET_SPARSE("sddmm: O", O, &O)) return;
+    if (get2d("sddmm: X", X_rank, X_ptr, &X) || get2d("sddmm: D", D_rank, D_ptr, &D)) return;
+    if (S.fmt != F_CSR || O.fmt != F_CSR) { fail("sddmm: S and O must be CSR"); return; }
+    const int64_t k = X.cols;
+    if (X.rows < S.nrows || (k > 1 && X.s1 != 1) || X.s0 < k) { fail("sddmm: X must be row-major [rows, K]"); return; }
+    if (D.rows != k || D.cols < S.ncols) { fail("sddmm: D must have sizes {K, cols}"); return; }
+    cudaStream_t st;
+    if (need_stream(&st)) return;
+    DevBag bag(st);
+    DevSparse dS;
+    if (upload_sparse("sddmm", S, bag, &dS)) return;
+    double *dX, *dY, *dOut;
+    if (bag.upload((void **)&dX, X.data, S.nrows > 0 ? (size_t)((S.nrows - 1) * X.s0 + k) * 8 : 0)) return;
+    int64_t ldy;
+    if (D.s0 == 1 && D.s1 >= k) {            // a row-major [cols, K] matrix viewed transposed
+        ldy = D.s1;
+        if (bag.upload((void **)&dY, D.data, S.ncols > 0 ? (size_t)((S.ncols - 1) * ldy + k) * 8 : 0)) return;
+    } else if (D.s1 == 1 && D.s0 >= D.cols) {   // D[k, j]: transpose on the device
+        double *dD;
+        if (bag.upload((void **)&dD, D.data, k > 0 ? (size_t)((k - 1) * D.s0 + S.ncols) * 8 : 0)) return;
+        ldy = k + (k & 1);
+        if (bag.alloc((void **)&dY, (size_t)S.ncols * ldy * 8)) return;
+        if (comet_b200_dev_transpose_f64(k, S.ncols, dD, D.s0, dY, ldy, st)) return;
+    } else {
+        fail("sddmm: D must be contiguous along one of its dimensions");
+        return;
+    }
+    if (bag.alloc((void **)&dOut, (size_t)S.nnz * 8)) return;
+    if (comet_b200_dev_sddmm_f64_i64(S.nrows, S.nnz, k, dS.pos, dS.crd, dS.val, dX, X.s0, dY, ldy, dOut, st))
+        return;
+    if (S.nnz && cudaMemcpyAsync(O.val, dOut, (size_t)S.nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+        fail("sddmm: copy of the result failed");
+        return;
+    }
+    copy_pattern(S, O);
+    finish(st);
+}
+
+void comet_b200_elews_mul_sparse_dense_f64_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                                               COMET_B200_SPARSE2D(C))
+{
+    UNUSED_TILES(A);
+    UNUSED_TILES(C);
+    clear_error();
+    HostSparse A, C;
+    Mat B;
+    if (GET_SPARSE("elews_mul: A", A, &A) || GET_SPARSE("elews_mul: C", C, &C)) return;
+    if (get2d("elews_mul: B", B_rank, B_ptr, &B)) return;
+    if (A.fmt == F_DCSR || C.fmt != A.fmt) { fail("elews_mul: A and C must both be CSR or both COO"); return; }
+    if (B.rows < A.nrows || B.cols < A.ncols || (B.cols > 1 && B.s1 != 1)) { fail("elews_mul: B must be row-major [rows, cols]"); return; }
+    cudaStream_t st;
+    if (need_stream(&st)) return;
+    DevBag bag(st);
+    DevSparse dA;
+    memset(&dA, 0, sizeof(dA));
+    if (bag.upload((void **)&dA.crd, A.a2crd, (size_t)A.nnz * 8)) return;
+    if (bag.upload((void **)&dA.val, A.val, (size_t)A.nnz * 8)) return;
+    if (A.fmt == F_CSR) { if (bag.upload((void **)&dA.pos, A.a2pos, (size_t)(A.nrows + 1) * 8)) return; }
+    else { if (bag.upload((void **)&dA.rows, A.a1crd, (size_t)A.nnz * 8)) return; }
+    double *dB, *dOut;
+    if (bag.upload((void **)&dB, B.data, A.nrows > 0 ? (size_t)((A.nrows - 1) * B.s0 + A.ncols) * 8 : 0)) return;
+    if (bag.alloc((void **)&dOut, (size_t)A.nnz * 8)) return;
+    if (comet_b200_dev_elews_mul_sparse_dense_f64_i64(A.nrows, A.nnz, dA.pos, dA.rows, dA.crd, dA.val, dB,
+                                                      B.s0, dOut, st))
+        return;
+    if (A.nnz && cudaMemcpyAsync(C.val, dOut, (size_t)A.nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+        fail("elews_mul: copy of the result failed");
+        return;
+    }
+    copy_pattern(A, C);
+    finish(st);
+}
+
+static int64_t sparse_out_symbolic(int kind, const HostSparse &A, const HostSparse &B,
+                                   const HostSparse *M, int semiring, Arr cpos, int64_t sizes_rank,
+                                   void *sizes_ptr)
+{
+    if (A.fmt != F_CSR || B.fmt != F_CSR || (M && M->fmt != F_CSR))
+        return fail("sparse output: operands must be CSR (COMET's workspace transformation handles CSR only)"), 0;
+    if (cpos.n < A.nrows + 1) return fail("sparse output: C2pos shorter than rows+1"), 0;
+    if (kind == 0 && B.nrows < A.ncols) return fail("spgemm: B has fewer rows than A has columns"), 0;
+    if (kind == 1 && (B.nrows != A.nrows)) return fail("elews_mul: row counts differ"), 0;
+    cudaStream_t st;
+    if (need_stream(&st)) return 0;
+    DevBag bag(st);
+    DevSparse dA, dB, dM;
+    memset(&dM, 0, sizeof(dM));
+    if (upload_sparse("A", A, bag, &dA)) return 0;
+    bool same = B.a2pos == A.a2pos && B.a2crd == A.a2crd && B.val == A.val;
+    if (same) dB = dA;
+    else if (upload_sparse("B", B, bag, &dB)) return 0;
+    if (M) {
+        if (M->a2pos == A.a2pos && M->a2crd == A.a2crd) dM = dA;
+        else if (M->a2pos == B.a2pos && M->a2crd == B.a2crd) dM = dB;
+        else if (upload_sparse("M", *M, bag, &dM, false)) return 0;
+    }
+    int64_t *dcpos;
+    if (bag.alloc((void **)&dcpos, (size_t)(A.nrows + 1) * 8)) return 0;
+    int64_t nnz = 0, dev_handle = 0;
+    int rc;
+    if (kind == 0)
+        rc = comet_b200_dev_spgemm_symbolic_f64_i64(A.nrows, B.ncols, B.nnz, dA.pos, dA.crd, dA.val,
+                                                    dB.pos, dB.crd, dB.val, M ? dM.pos : nullptr,
+                                                    M ? dM.crd : nullptr, semiring, dcpos, &nnz,
+                                                    &dev_handle, st);
+    else
+        rc = comet_b200_dev_elews_mul_sparse_sparse_symbolic_f64_i64(
+            A.nrows, dA.pos, dA.crd, dA.val, dB.pos, dB.crd, dB.val, dcpos, &nnz, &dev_handle, st);
+    if (rc) return 0;
+    if (cudaMemcpyAsync(cpos.data, dcpos, (size_t)(A.nrows + 1) * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess) {
+        comet_b200_handle_destroy(dev_handle);
+        return fail("sparse output: copy of C2pos failed"), 0;
+    }
+    fill_sizes(sizes_ptr, sizes_rank, A.nrows, kind == 0 ? B.ncols : A.ncols, nnz);
+    HostPlan *hp = new HostPlan();
+    hp->dev_handle = dev_handle;
+    hp->nnz = nnz;
+    hp->owned.swap(bag.ptrs);   // staged operands live until the numeric call
+    std::lock_guard<std::mutex> lk(g_hp_mu);
+    g_hplans[dev_handle] = hp;
+    return dev_handle;
+}
+
+int64_t comet_b200_spgemm_symbolic_f64_i64(COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
+                                           COMET_B200_SPARSE2D(M), int32_t mask_type,
+                                           int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr,
+                                           int64_t sizes_rank, void *sizes_ptr)
+{
+    UNUSED_TILES(A);
+    UNUSED_TILES(B);
+    UNUSED_TILES(M);
+    clear_error();
+    HostSparse A, B, M;
+    Arr cpos;
+    if (GET_SPARSE("spgemm: A", A, &A) || GET_SPARSE("spgemm: B", B, &B)) return 0;
+    if (mask_type != COMET_B200_MASK_NONE && mask_type != COMET_B200_MASK_PUSH) {
+        fail("spgemm: unsupported mask type %d (none and push are handled)", mask_type);
+        return 0;
+    }
+    bool masked = mask_type == COMET_B200_MASK_PUSH;
+    if (masked && GET_SPARSE("spgemm: M", M, &M)) return 0;
+    if (get1d("spgemm: C2pos", C2pos_rank, C2pos_ptr, 8, &cpos)) return 0;
+    return sparse_out_symbolic(0, A, B, masked ? &M : nullptr, semiring, cpos, sizes_rank, sizes_ptr);
+}
+
+int64_t comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64(COMET_B200_SPARSE2D(A),
+                                                            COMET_B200_SPARSE2D(B),
+                                                            int64_t C2pos_rank, void *C2pos_ptr,
+                                                            int64_t sizes_rank, void *sizes_ptr)
+{
+    UNUSED_TILES(A);
+    UNUSED_TILES(B);
+    clear_error();
+    HostSparse A, B;
+    Arr cpos;
+    if (GET_SPARSE("elews_mul: A", A, &A) || GET_SPARSE("elews_mul: B", B, &B)) return 0;
+    if (get1d("elews_mul: C2pos", C2pos_rank, C2pos_ptr, 8, &cpos)) return 0;
+    return sparse_out_symbolic(1, A, B, nullptr, COMET_B200_PLUS_TIMES, cpos, sizes_rank, sizes_ptr);
+}
+
+void comet_b200_spgemm_numeric_f64_i64(int64_t handle, int64_t C2crd_rank, void *C2crd_ptr,
+                                       int64_t Cval_rank, void *Cval_ptr)
+{
+    clear_error();
+    HostPlan *hp = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_hp_mu);
+        auto it = g_hplans.find(handle);
+        if (it != g_hplans.end()) { hp = it->second; g_hplans.erase(it); }
+    }
+    if (!hp) { fail("numeric phase: unknown handle %lld", (long long)handle); return; }
+    cudaStream_t st = lib_stream();
+    Arr crd, val;
+    int rc = get1d("C2crd", C2crd_rank, C2crd_ptr, 8, &crd) || get1d("Cval", Cval_rank, Cval_ptr, 8, &val);
+    if (!rc && (crd.n < hp->nnz || val.n < hp->nnz)) rc = fail("numeric phase: C2crd/Cval shorter than nnz");
+    int64_t *dcrd = nullptr;
+    double *dval = nullptr;
+    if (!rc && cudaMallocAsync((void **)&dcrd, (size_t)(hp->nnz ? hp->nnz : 1) * 8, st) != cudaSuccess)
+        rc = fail("numeric phase: device allocation failed");
+    if (!rc && cudaMallocAsync((void **)&dval, (size_t)(hp->nnz ? hp->nnz : 1) * 8, st) != cudaSuccess)
+        rc = fail("numeric phase: device allocation failed");
+    if (!rc) rc = comet_b200_dev_spgemm_numeric_f64_i64(hp->dev_handle, dcrd, dval, 0, st);
+    else comet_b200_handle_destroy(hp->dev_handle);
+    if (!rc && hp->nnz) {
+        if (cudaMemcpyAsync(crd.data, dcrd, (size_t)hp->nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+            cudaMemcpyAsync(val.data, dval, (size_t)hp->nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+            rc = fail("numeric phase: copy of the result failed");
+    }
+    if (cudaStreamSynchronize(st) != cudaSuccess && !rc) fail("numeric phase: synchronize failed");
+    if (dcrd) cudaFreeAsync(dcrd, st);
+    if (dval) cudaFreeAsync(dval, st);
+    for (void *p : hp->owned) cudaFreeAsync(p, st);
+    delete hp;
+}
+
+void comet_b200_masked_spgemm_count_f64_i64(COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
+                                            COMET_B200_SPARSE2D(M), int32_t mask_type,
+                                            int32_t semiring, int64_t out_rank, void *out_ptr)
+{
+    UNUSED_TILES(A);
+    UNUSED_TILES(B);
+    UNUSED_TILES(M);
+    clear_error();
+    HostSparse A, B, M;
+    Arr out;
+    if (GET_SPARSE("masked count: A", A, &A) || GET_SPARSE("masked count: B", B, &B) ||
+        GET_SPARSE("masked count: M", M, &M))
+        return;
+    if (get1d("masked count: out", out_rank, out_ptr, 8, &out) || out.n < 1) { fail("masked count: out must hold one int64"); return; }
+    if (mask_type != COMET_B200_MASK_PUSH || semiring != COMET_B200_PLUS_PAIR) {
+        fail("masked count: only the push mask with the plus-pair semiring is handled");
+        return;
+    }
+    if (A.fmt != F_CSR || B.fmt != F_CSR || M.fmt != F_CSR) { fail("masked count: operands must be CSR"); return; }
+    if (B.nrows < A.ncols || M.nrows < A.nrows) { fail("masked count: shapes do not match"); return; }
+    cudaStream_t st;
+    if (need_stream(&st)) return;
+    DevBag bag(st);
+    DevSparse dA, dB, dM;
+    if (upload_sparse("A", A, bag, &dA, false)) return;
+    if (B.a2pos == A.a2pos && B.a2crd == A.a2crd) dB = dA;
+    else if (upload_sparse("B", B, bag, &dB, false)) return;
+    if (M.a2pos == A.a2pos && M.a2crd == A.a2crd) dM = dA;
+    else if (M.a2pos == B.a2pos && M.a2crd == B.a2crd) dM = dB;
+    else if (upload_sparse("M", M, bag, &dM, false)) return;
+    int64_t *dcount;
+    if (bag.alloc((void **)&dcount, 8)) return;
+    if (comet_b200_dev_masked_spgemm_count_f64_i64(0, A.nrows, B.ncols, A.nnz, B.nnz, M.nnz, dA.pos, dA.crd,
+                                                   dB.pos, dB.crd, dM.pos, dM.crd, dcount, st))
+        return;
+    if (cudaMemcpyAsync(out.data, dcount, 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) { fail("masked count: copy failed"); return; }
+    finish(st);
+}
+
+}  // extern "C"

@@ -1,0 +1,663 @@
+// Gustavson SpGEMM  C = A*B  (optionally C<M,push> = A*B), all CSR, f64 / i64,
+// as a symbolic call (fills C.pos) and a numeric call (fills C.crd sorted, C.val).
+//
+// Rows are binned by an upper bound on their number of distinct columns
+// (sum of the lengths of the B rows they touch, capped by the mask row):
+//   bin 0  no products                     -> empty row
+//   bin 1  bound <= HASH_ROW_MAX           -> one warp per row, hash table in
+//          shared memory (int32 keys + f64 accumulators); output order by rank
+//          counting among the row's distinct keys
+//   bin 2  everything else                 -> one CTA per row, a bitmap over the
+//          columns of B in shared memory (global memory when B has too many
+//          columns); popcounts give the row's count, prefix popcounts give each
+//          column's rank, so crd comes out sorted with no sort and val[rank] is
+//          accumulated in place with f64 atomics on the output row, which the
+//          CTA has just zeroed and which therefore sits in L2.
+// This mirrors COMET's workspace transformation (dense row workspace + mark
+// array, sort of the touched columns) with a bit per column instead of a mark
+// word per column, and replaces std::sort by ranking.
+//
+// The bitmaps of bin-2 rows found by the symbolic call are kept (when they fit
+// a budget) so that the numeric call does not have to traverse the products a
+// second time to rebuild them.
+//
+// Accumulation order inside a row is not fixed (atomics); structure (pos, crd)
+// is exact and values agree with a sequential sum to rounding.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace cb200 {
+
+static const int HASH_ROW_MAX = 256;        // bound for bin 1
+static const int HASH_SLOTS = 512;          // table size per warp (load factor <= 0.5)
+static const int HASH_WARPS = 4;            // warps per CTA in the hash kernels
+static const int BM_THREADS = 512;          // CTA size of the bitmap kernels
+static const size_t BM_SMEM_LIMIT = 200 * 1024;
+static const size_t BM_STORE_BUDGET = (size_t)12 << 30;
+
+struct Plan {
+    int kind;                // 0 = spgemm, 1 = elementwise CSR .* CSR
+    int64_t nrows, ncols, nnz_b;
+    const int64_t *apos, *acrd, *bpos, *bcrd, *mpos, *mcrd;
+    const double *aval, *bval;
+    int pair;
+    int64_t *cpos;           // caller's array
+    int64_t nnz_c;
+    // owned device memory
+    int32_t *bcrd32;
+    int64_t *cnt;            // per-row distinct count
+    int32_t *list1, *list2;  // rows of bin 1 / bin 2
+    unsigned *bin_counts;    // [2] on device
+    unsigned n1, n2;
+    uint32_t *bm_store;      // n2 * words, or null
+    int words;
+};
+
+static std::mutex g_plans_mu;
+static std::unordered_map<int64_t, Plan *> g_plans;
+static int64_t g_next_handle = 1;
+
+static void plan_free(Plan *p, cudaStream_t st)
+{
+    if (!p) return;
+    if (p->bcrd32) cudaFreeAsync(p->bcrd32, st);
+    if (p->cnt) cudaFreeAsync(p->cnt, st);
+    if (p->list1) cudaFreeAsync(p->list1, st);
+    if (p->list2) cudaFreeAsync(p->list2, st);
+    if (p->bin_counts) cudaFreeAsync(p->bin_counts, st);
+    if (p->bm_store) cudaFreeAsync(p->bm_store, st);
+    delete p;
+}
+
+static int pool_setup()
+{
+    static bool done[64] = {false};
+    int d = 0;
+    CB_CUDA(cudaGetDevice(&d));
+    if (d >= 0 && d < 64 && !done[d]) {
+        cudaMemPool_t pool;
+        CB_CUDA(cudaDeviceGetDefaultMemPool(&pool, d));
+        uint64_t keep = ~(uint64_t)0;   // keep freed blocks cached for the next call
+        CB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        done[d] = true;
+    }
+    return 0;
+}
+
+template <typename T>
+static int dev_alloc(T **p, size_t n, cudaStream_t st)
+{
+    if (n == 0) n = 1;
+    cudaError_t e = cudaMallocAsync((void **)p, n * sizeof(T), st);
+    if (e != cudaSuccess) {
+        *p = nullptr;
+        return fail("device allocation of %zu bytes failed: %s", n * sizeof(T), cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+// --------------------------------------------------------------------------
+// mask membership: is column j stored in the (ascending) mask row [ms, me)?
+// --------------------------------------------------------------------------
+__device__ __forceinline__ bool in_mask(const int64_t *__restrict__ mcrd, int64_t ms, int64_t me,
+                                        int64_t j)
+{
+    while (ms < me) {
+        int64_t mid = (ms + me) >> 1;
+        int64_t v = mcrd[mid];
+        if (v == j) return true;
+        if (v < j) ms = mid + 1; else me = mid;
+    }
+    return false;
+}
+
+// --------------------------------------------------------------------------
+// Binning: 8 lanes per row sum the lengths of the B rows it touches.
+// --------------------------------------------------------------------------
+static const int BIN_THREADS = 256;
+static const int BIN_ROWS = (BIN_THREADS / 8) * 4;
+
+__global__ void __launch_bounds__(BIN_THREADS)
+bin_rows_kernel(int64_t nrows, const int64_t *__restrict__ apos, const int64_t *__restrict__ acrd,
+                const int64_t *__restrict__ bpos, const int64_t *__restrict__ mpos,
+                int64_t *__restrict__ cnt, int32_t *__restrict__ list1, int32_t *__restrict__ list2,
+                unsigned *__restrict__ bin_counts)
+{
+    __shared__ unsigned char bin_of[BIN_ROWS];
+    __shared__ unsigned short local_at[BIN_ROWS];
+    __shared__ unsigned local_cnt[2], base[2];
+    const int g = threadIdx.x / 8, l = threadIdx.x % 8;
+    const unsigned gmask = 0xffu << ((threadIdx.x & 31) & ~7);
+    if (threadIdx.x < 2) local_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t row0 = (int64_t)blockIdx.x * BIN_ROWS;
+    for (int pass = 0; pass < 4; pass++) {
+        int slot = pass * (BIN_THREADS / 8) + g;
+        int64_t r = row0 + slot;
+        if (r >= nrows) break;
+        int64_t ub = 0;
+        for (int64_t p = apos[r] + l; p < apos[r + 1]; p += 8) {
+            int64_t k = acrd[p];
+            ub += bpos[k + 1] - bpos[k];
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) ub += __shfl_xor_sync(gmask, (long long)ub, o, 8);
+        if (mpos) {
+            int64_t ml = mpos[r + 1] - mpos[r];
+            if (ml < ub) ub = ml;
+        }
+        if (l == 0) {
+            int b = ub == 0 ? 0 : (ub <= HASH_ROW_MAX ? 1 : 2);
+            bin_of[slot] = (unsigned char)b;
+            if (b == 0) cnt[r] = 0;
+            else local_at[slot] = (unsigned short)atomicAdd(&local_cnt[b - 1], 1u);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2) base[threadIdx.x] = atomicAdd(&bin_counts[threadIdx.x], local_cnt[threadIdx.x]);
+    __syncthreads();
+    for (int slot = threadIdx.x; slot < BIN_ROWS; slot += BIN_THREADS) {
+        int64_t r = row0 + slot;
+        if (r >= nrows) break;
+        int b = bin_of[slot];
+        if (b == 1) list1[base[0] + local_at[slot]] = (int32_t)r;
+        else if (b == 2) list2[base[1] + local_at[slot]] = (int32_t)r;
+    }
+}
+
+// --------------------------------------------------------------------------
+// Bin 1: warp per row, hash table in shared memory.
+// --------------------------------------------------------------------------
+__device__ __forceinline__ int hash_slot(int32_t j)
+{
+    return (int)(((uint32_t)j * 0x9E3779B1u) >> 23);   // top 9 bits: 0..511
+}
+
+// Inserts j; returns the slot, sets *fresh when this call created the entry.
+__device__ __forceinline__ int hash_insert(int32_t *keys, int32_t j, bool *fresh)
+{
+    int h = hash_slot(j);
+    *fresh = false;
+    for (int probe = 0; probe < HASH_SLOTS; probe++) {
+        int32_t old = atomicCAS(&keys[h], -1, j);
+        if (old == -1) { *fresh = true; return h; }
+        if (old == j) return h;
+        h = (h + 1) & (HASH_SLOTS - 1);
+    }
+    return -1;   // cannot happen: at most HASH_ROW_MAX distinct keys in HASH_SLOTS slots
+}
+
+template <bool NUMERIC>
+__global__ void __launch_bounds__(HASH_WARPS * 32)
+hash_rows_kernel(unsigned nlist, const int32_t *__restrict__ list, const int64_t *__restrict__ apos,
+                 const int64_t *__restrict__ acrd, const double *__restrict__ aval,
+                 const int64_t *__restrict__ bpos, const int32_t *__restrict__ bcrd,
+                 const double *__restrict__ bval, const int64_t *__restrict__ mpos,
+                 const int64_t *__restrict__ mcrd, int pair, int64_t *__restrict__ cnt,
+                 const int64_t *__restrict__ cpos, int64_t *__restrict__ ccrd,
+                 double *__restrict__ cval)
+{
+    __shared__ int32_t s_keys[HASH_WARPS][HASH_SLOTS];
+    __shared__ double s_vals[NUMERIC ? HASH_WARPS : 1][NUMERIC ? HASH_SLOTS : 1];
+    __shared__ int32_t s_ckeys[NUMERIC ? HASH_WARPS : 1][NUMERIC ? HASH_ROW_MAX : 1];
+    __shared__ unsigned short s_cslot[NUMERIC ? HASH_WARPS : 1][NUMERIC ? HASH_ROW_MAX : 1];
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int32_t *keys = s_keys[w];
+    const unsigned nwarps = gridDim.x * HASH_WARPS;
+    for (unsigned it = blockIdx.x * HASH_WARPS + w; it < nlist; it += nwarps) {
+        const int64_t r = list[it];
+        for (int s = lane; s < HASH_SLOTS; s += 32) {
+            keys[s] = -1;
+            if (NUMERIC) s_vals[w][s] = 0.0;
+        }
+        __syncwarp();
+        int64_t ms = 0, me = 0;
+        if (mpos) { ms = mpos[r]; me = mpos[r + 1]; }
+        int fresh_count = 0;
+        for (int64_t p = apos[r]; p < apos[r + 1]; p++) {
+            const int64_t k = acrd[p];
+            const double av = NUMERIC ? aval[p] : 0.0;
+            for (int64_t q = bpos[k] + lane; q < bpos[k + 1]; q += 32) {
+                int32_t j = bcrd[q];
+                if (mpos && !in_mask(mcrd, ms, me, j)) continue;
+                bool fresh;
+                int h = hash_insert(keys, j, &fresh);
+                fresh_count += fresh ? 1 : 0;
+                if (NUMERIC && h >= 0) atomicAdd(&s_vals[w][h], pair ? 1.0 : av * bval[q]);
+            }
+        }
+        __syncwarp();
+        if (!NUMERIC) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) fresh_count += __shfl_xor_sync(0xffffffffu, fresh_count, o);
+            if (lane == 0) cnt[r] = fresh_count;
+        } else {
+            // compact the occupied slots, then place each key at its rank among them
+            int n = 0;
+            for (int s0 = 0; s0 < HASH_SLOTS; s0 += 32) {
+                int32_t key = keys[s0 + lane];
+                unsigned occ = __ballot_sync(0xffffffffu, key != -1);
+                if (key != -1) {
+                    int at = n + __popc(occ & ((1u << lane) - 1u));
+                    s_ckeys[w][at] = key;
+                    s_cslot[w][at] = (unsigned short)(s0 + lane);
+                }
+                n += __popc(occ);
+            }
+            __syncwarp();
+            const int64_t base = cpos[r];
+            for (int i = lane; i < n; i += 32) {
+                int32_t key = s_ckeys[w][i];
+                int rank = 0;
+                for (int t = 0; t < n; t++) rank += s_ckeys[w][t] < key ? 1 : 0;
+                ccrd[base + rank] = key;
+                cval[base + rank] = s_vals[w][s_cslot[w][i]];
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// --------------------------------------------------------------------------
+// Bin 2: CTA per row, bitmap over B's columns.
+// --------------------------------------------------------------------------
+__device__ __forceinline__ unsigned block_sum_u32(unsigned v, unsigned *s_warp)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = v;
+    __syncthreads();
+    unsigned t = 0;
+    for (int i = 0; i < BM_THREADS / 32; i++) t += s_warp[i];
+    return t;
+}
+
+// marks the columns of row r's products in bm (bm cleared by the caller)
+__device__ __forceinline__ void mark_products(uint32_t *bm, int64_t r, const int64_t *__restrict__ apos,
+                                              const int64_t *__restrict__ acrd,
+                                              const int64_t *__restrict__ bpos,
+                                              const int32_t *__restrict__ bcrd,
+                                              const int64_t *__restrict__ mpos,
+                                              const int64_t *__restrict__ mcrd)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int64_t ms = 0, me = 0;
+    if (mpos) { ms = mpos[r]; me = mpos[r + 1]; }
+    for (int64_t p = apos[r] + warp; p < apos[r + 1]; p += BM_THREADS / 32) {
+        const int64_t k = acrd[p];
+        for (int64_t q = bpos[k] + lane; q < bpos[k + 1]; q += 32) {
+            int32_t j = bcrd[q];
+            if (mpos && !in_mask(mcrd, ms, me, j)) continue;
+            atomicOr(&bm[j >> 5], 1u << (j & 31));
+        }
+    }
+}
+
+template <bool SMEM>
+__global__ void __launch_bounds__(BM_THREADS)
+bitmap_symbolic_kernel(unsigned nlist, const int32_t *__restrict__ list, int words,
+                       uint32_t *__restrict__ gbm, const int64_t *__restrict__ apos,
+                       const int64_t *__restrict__ acrd, const int64_t *__restrict__ bpos,
+                       const int32_t *__restrict__ bcrd, const int64_t *__restrict__ mpos,
+                       const int64_t *__restrict__ mcrd, int64_t *__restrict__ cnt,
+                       uint32_t *__restrict__ bm_store)
+{
+    extern __shared__ uint32_t s_dyn[];
+    __shared__ unsigned s_warp[BM_THREADS / 32];
+    uint32_t *bm = SMEM ? s_dyn : gbm + (size_t)blockIdx.x * words;
+    for (unsigned it = blockIdx.x; it < nlist; it += gridDim.x) {
+        const int64_t r = list[it];
+        for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = 0;
+        __syncthreads();
+        mark_products(bm, r, apos, acrd, bpos, bcrd, mpos, mcrd);
+        __syncthreads();
+        unsigned c = 0;
+        uint32_t *keep = bm_store ? bm_store + (size_t)it * words : nullptr;
+        for (int w = threadIdx.x; w < words; w += BM_THREADS) {
+            uint32_t v = bm[w];
+            c += __popc(v);
+            if (keep) keep[w] = v;
+        }
+        unsigned total = block_sum_u32(c, s_warp);
+        if (threadIdx.x == 0) cnt[r] = total;
+        __syncthreads();
+    }
+}
+
+template <bool SMEM>
+__global__ void __launch_bounds__(BM_THREADS)
+bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int words,
+                      uint32_t *__restrict__ gbm, const int64_t *__restrict__ apos,
+                      const int64_t *__restrict__ acrd, const double *__restrict__ aval,
+                      const int64_t *__restrict__ bpos, const int32_t *__restrict__ bcrd,
+                      const double *__restrict__ bval, const int64_t *__restrict__ mpos,
+                      const int64_t *__restrict__ mcrd, int pair,
+                      const uint32_t *__restrict__ bm_store, const int64_t *__restrict__ cpos,
+                      int64_t *__restrict__ ccrd, double *__restrict__ cval)
+{
+    extern __shared__ uint32_t s_dyn[];
+    __shared__ unsigned s_warp[BM_THREADS / 32];
+    __shared__ unsigned s_scan[BM_THREADS];
+    uint32_t *bm = SMEM ? s_dyn : gbm + (size_t)blockIdx.x * 2 * words;
+    uint32_t *pre = bm + words;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per = (words + BM_THREADS - 1) / BM_THREADS;   // words per thread, contiguous
+    for (unsigned it = blockIdx.x; it < nlist; it += gridDim.x) {
+        const int64_t r = list[it];
+        if (bm_store) {
+            const uint32_t *keep = bm_store + (size_t)it * words;
+            for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = keep[w];
+            __syncthreads();
+        } else {
+            for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = 0;
+            __syncthreads();
+            mark_products(bm, r, apos, acrd, bpos, bcrd, mpos, mcrd);
+            __syncthreads();
+        }
+        // exclusive prefix popcount per word
+        const int w0 = threadIdx.x * per, w1 = min(w0 + per, words);
+        unsigned mine = 0;
+        for (int w = w0; w < w1; w++) mine += __popc(bm[w]);
+        s_scan[threadIdx.x] = mine;
+        __syncthreads();
+        // Hillis-Steele inclusive scan over BM_THREADS partial sums
+        for (int o = 1; o < BM_THREADS; o <<= 1) {
+            unsigned t = threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0;
+            __syncthreads();
+            s_scan[threadIdx.x] += t;
+            __syncthreads();
+        }
+        unsigned run = s_scan[threadIdx.x] - mine;
+        const int64_t base = cpos[r];
+        const int64_t rown = cpos[r + 1] - base;
+        for (int w = w0; w < w1; w++) {
+            uint32_t v = bm[w];
+            pre[w] = run;
+            while (v) {
+                int b = __ffs(v) - 1;
+                v &= v - 1;
+                ccrd[base + run] = (int64_t)w * 32 + b;
+                run++;
+            }
+        }
+        for (int64_t t = threadIdx.x; t < rown; t += BM_THREADS) cval[base + t] = 0.0;
+        __syncthreads();
+        // accumulate every product at the rank of its column
+        for (int64_t p = apos[r] + warp; p < apos[r + 1]; p += BM_THREADS / 32) {
+            const int64_t k = acrd[p];
+            const double av = aval[p];
+            for (int64_t q = bpos[k] + lane; q < bpos[k + 1]; q += 32) {
+                int32_t j = bcrd[q];
+                uint32_t word = bm[j >> 5];
+                uint32_t bit = 1u << (j & 31);
+                if (!(word & bit)) continue;   // filtered out by the mask
+                unsigned rank = pre[j >> 5] + __popc(word & (bit - 1u));
+                atomicAdd(&cval[base + rank], pair ? 1.0 : av * bval[q]);
+            }
+        }
+        __syncthreads();
+    }
+    (void)s_warp; (void)mpos; (void)mcrd;
+}
+
+// --------------------------------------------------------------------------
+// Elementwise CSR .* CSR: two-pointer intersection, one thread per row.
+// --------------------------------------------------------------------------
+template <bool NUMERIC>
+__global__ void __launch_bounds__(256)
+elews_ss_kernel(int64_t nrows, const int64_t *__restrict__ apos, const int64_t *__restrict__ acrd,
+                const double *__restrict__ aval, const int64_t *__restrict__ bpos,
+                const int64_t *__restrict__ bcrd, const double *__restrict__ bval,
+                int64_t *__restrict__ cnt, const int64_t *__restrict__ cpos,
+                int64_t *__restrict__ ccrd, double *__restrict__ cval)
+{
+    int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= nrows) return;
+    int64_t p = apos[r], pe = apos[r + 1], q = bpos[r], qe = bpos[r + 1];
+    int64_t n = 0, at = NUMERIC ? cpos[r] : 0;
+    while (p < pe && q < qe) {
+        int64_t ca = acrd[p], cb = bcrd[q];
+        if (ca == cb) {
+            if (NUMERIC) { ccrd[at + n] = ca; cval[at + n] = aval[p] * bval[q]; }
+            n++;
+        }
+        if (ca <= cb) p++;
+        if (cb <= ca) q++;
+    }
+    if (!NUMERIC) cnt[r] = n;
+}
+
+// --------------------------------------------------------------------------
+// Host side
+// --------------------------------------------------------------------------
+static int64_t register_plan(Plan *p)
+{
+    std::lock_guard<std::mutex> lk(g_plans_mu);
+    int64_t h = g_next_handle++;
+    g_plans[h] = p;
+    return h;
+}
+
+static Plan *find_plan(int64_t h, bool remove)
+{
+    std::lock_guard<std::mutex> lk(g_plans_mu);
+    auto it = g_plans.find(h);
+    if (it == g_plans.end()) return nullptr;
+    Plan *p = it->second;
+    if (remove) g_plans.erase(it);
+    return p;
+}
+
+static int bitmap_grid(unsigned nlist, size_t smem_bytes)
+{
+    int per_sm = smem_bytes ? (int)((220 * 1024) / (smem_bytes + 1024)) : 2;
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 2048 / BM_THREADS) per_sm = 2048 / BM_THREADS;
+    int64_t g = (int64_t)sm_count() * per_sm;
+    if (g > nlist) g = nlist;
+    return (int)(g < 1 ? 1 : g);
+}
+
+int spgemm_symbolic(int64_t nrows, int64_t ncols_b, int64_t nnz_b, const int64_t *apos,
+                    const int64_t *acrd, const double *aval, const int64_t *bpos,
+                    const int64_t *bcrd, const double *bval, const int64_t *mpos,
+                    const int64_t *mcrd, int semiring, int64_t *cpos, int64_t *nnz_host,
+                    int64_t *handle_out, cudaStream_t st)
+{
+    if (ncols_b >= 0x7fffffffLL || nrows >= 0x7fffffffLL)
+        return fail("spgemm: more than 2^31-1 rows or columns is not supported");
+    if (((uintptr_t)bcrd & 15) != 0) return fail("spgemm: B.crd must be 16-byte aligned");
+    CB_TRY(pool_setup());
+    Plan *p = new Plan();
+    memset(p, 0, sizeof(Plan));
+    p->kind = 0; p->nrows = nrows; p->ncols = ncols_b; p->nnz_b = nnz_b;
+    p->apos = apos; p->acrd = acrd; p->aval = aval; p->bpos = bpos; p->bcrd = bcrd; p->bval = bval;
+    p->mpos = mpos; p->mcrd = mpos ? mcrd : nullptr; p->pair = semiring == COMET_B200_PLUS_PAIR;
+    p->cpos = cpos;
+    p->words = (int)ceil_div(ncols_b, 32);
+    int rc = 0;
+#define STEP(expr) do { if (!rc) rc = (expr); } while (0)
+#define STEP_CUDA(expr) do { if (!rc) { cudaError_t e_ = (expr); if (e_ != cudaSuccess) rc = fail("%s failed: %s", #expr, cudaGetErrorString(e_)); } } while (0)
+    STEP(dev_alloc(&p->bcrd32, (size_t)nnz_b, st));
+    STEP(dev_alloc(&p->cnt, (size_t)nrows + 1, st));
+    STEP(dev_alloc(&p->list1, (size_t)nrows, st));
+    STEP(dev_alloc(&p->list2, (size_t)nrows, st));
+    STEP(dev_alloc(&p->bin_counts, 2, st));
+    STEP_CUDA(cudaMemsetAsync(p->bin_counts, 0, 2 * sizeof(unsigned), st));
+    STEP(narrow_i64_to_i32(bcrd, p->bcrd32, nnz_b, st));
+    if (!rc && nrows > 0) {
+        bin_rows_kernel<<<(unsigned)ceil_div(nrows, BIN_ROWS), BIN_THREADS, 0, st>>>(
+            nrows, apos, acrd, bpos, mpos, p->cnt, p->list1, p->list2, p->bin_counts);
+        STEP_CUDA(cudaGetLastError());
+    }
+    unsigned counts[2] = {0, 0};
+    STEP_CUDA(cudaMemcpyAsync(counts, p->bin_counts, sizeof(counts), cudaMemcpyDeviceToHost, st));
+    STEP_CUDA(cudaStreamSynchronize(st));
+    p->n1 = counts[0]; p->n2 = counts[1];
+    if (!rc && p->n1) {
+        unsigned grid = (unsigned)ceil_div(p->n1, HASH_WARPS);
+        unsigned cap = (unsigned)sm_count() * 16;
+        if (grid > cap) grid = cap;
+        hash_rows_kernel<false><<<grid, HASH_WARPS * 32, 0, st>>>(
+            p->n1, p->list1, apos, acrd, aval, bpos, p->bcrd32, bval, mpos, p->mcrd, p->pair, p->cnt,
+            nullptr, nullptr, nullptr);
+        STEP_CUDA(cudaGetLastError());
+    }
+    if (!rc && p->n2) {
+        size_t store = (size_t)p->n2 * p->words * sizeof(uint32_t);
+        if (store <= BM_STORE_BUDGET) {
+            cudaError_t e = cudaMallocAsync((void **)&p->bm_store, store, st);
+            if (e != cudaSuccess) { p->bm_store = nullptr; (void)cudaGetLastError(); }
+        }
+        size_t smem = (size_t)p->words * sizeof(uint32_t);
+        if (2 * smem <= BM_SMEM_LIMIT) {
+            int grid = bitmap_grid(p->n2, smem);
+            STEP_CUDA(cudaFuncSetAttribute(bitmap_symbolic_kernel<true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (!rc)
+                bitmap_symbolic_kernel<true><<<grid, BM_THREADS, smem, st>>>(
+                    p->n2, p->list2, p->words, nullptr, apos, acrd, bpos, p->bcrd32, mpos, p->mcrd,
+                    p->cnt, p->bm_store);
+        } else {
+            int grid = bitmap_grid(p->n2, 0);
+            void *gbm = nullptr;
+            STEP(scratch(SLOT_BITMAP, (size_t)grid * 2 * smem, &gbm));
+            if (!rc)
+                bitmap_symbolic_kernel<false><<<grid, BM_THREADS, 0, st>>>(
+                    p->n2, p->list2, p->words, (uint32_t *)gbm, apos, acrd, bpos, p->bcrd32, mpos,
+                    p->mcrd, p->cnt, p->bm_store);
+        }
+        STEP_CUDA(cudaGetLastError());
+    }
+    STEP(exclusive_scan_i64(p->cnt, cpos, nrows, st));
+    STEP_CUDA(cudaMemcpyAsync(&p->nnz_c, cpos + nrows, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    STEP_CUDA(cudaStreamSynchronize(st));
+#undef STEP
+#undef STEP_CUDA
+    if (rc) { plan_free(p, st); return rc; }
+    *nnz_host = p->nnz_c;
+    *handle_out = register_plan(p);
+    return 0;
+}
+
+int elews_ss_symbolic(int64_t nrows, const int64_t *apos, const int64_t *acrd, const double *aval,
+                      const int64_t *bpos, const int64_t *bcrd, const double *bval, int64_t *cpos,
+                      int64_t *nnz_host, int64_t *handle_out, cudaStream_t st)
+{
+    CB_TRY(pool_setup());
+    Plan *p = new Plan();
+    memset(p, 0, sizeof(Plan));
+    p->kind = 1; p->nrows = nrows;
+    p->apos = apos; p->acrd = acrd; p->aval = aval; p->bpos = bpos; p->bcrd = bcrd; p->bval = bval;
+    p->cpos = cpos;
+    int rc = dev_alloc(&p->cnt, (size_t)nrows + 1, st);
+    if (!rc && nrows > 0) {
+        elews_ss_kernel<false><<<(unsigned)ceil_div(nrows, 256), 256, 0, st>>>(
+            nrows, apos, acrd, aval, bpos, bcrd, bval, p->cnt, nullptr, nullptr, nullptr);
+        if (cudaGetLastError() != cudaSuccess) rc = fail("elews symbolic launch failed");
+    }
+    if (!rc) rc = exclusive_scan_i64(p->cnt, cpos, nrows, st);
+    if (!rc && cudaMemcpyAsync(&p->nnz_c, cpos + nrows, sizeof(int64_t), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+        rc = fail("elews symbolic: copy of nnz failed");
+    if (!rc && cudaStreamSynchronize(st) != cudaSuccess) rc = fail("elews symbolic: synchronize failed");
+    if (rc) { plan_free(p, st); return rc; }
+    *nnz_host = p->nnz_c;
+    *handle_out = register_plan(p);
+    return 0;
+}
+
+int sparse_out_numeric(int64_t handle, int64_t *ccrd, double *cval, int keep, cudaStream_t st)
+{
+    Plan *p = find_plan(handle, !keep);
+    if (!p) return fail("numeric phase: unknown handle %lld", (long long)handle);
+    int rc = 0;
+    if (p->kind == 1) {
+        if (p->nrows > 0) {
+            elews_ss_kernel<true><<<(unsigned)ceil_div(p->nrows, 256), 256, 0, st>>>(
+                p->nrows, p->apos, p->acrd, p->aval, p->bpos, p->bcrd, p->bval, nullptr, p->cpos, ccrd,
+                cval);
+            if (cudaGetLastError() != cudaSuccess) rc = fail("elews numeric launch failed");
+        }
+    } else {
+        if (p->n1) {
+            unsigned grid = (unsigned)ceil_div(p->n1, HASH_WARPS);
+            unsigned cap = (unsigned)sm_count() * 16;
+            if (grid > cap) grid = cap;
+            hash_rows_kernel<true><<<grid, HASH_WARPS * 32, 0, st>>>(
+                p->n1, p->list1, p->apos, p->acrd, p->aval, p->bpos, p->bcrd32, p->bval, p->mpos,
+                p->mcrd, p->pair, nullptr, p->cpos, ccrd, cval);
+            if (cudaGetLastError() != cudaSuccess) rc = fail("spgemm numeric (hash) launch failed");
+        }
+        if (!rc && p->n2) {
+            size_t smem = (size_t)p->words * sizeof(uint32_t) * 2;
+            if (smem <= BM_SMEM_LIMIT) {
+                int grid = bitmap_grid(p->n2, smem);
+                cudaFuncSetAttribute(bitmap_numeric_kernel<true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                bitmap_numeric_kernel<true><<<grid, BM_THREADS, smem, st>>>(
+                    p->n2, p->list2, p->words, nullptr, p->apos, p->acrd, p->aval, p->bpos, p->bcrd32,
+                    p->bval, p->mpos, p->mcrd, p->pair, p->bm_store, p->cpos, ccrd, cval);
+            } else {
+                int grid = bitmap_grid(p->n2, 0);
+                void *gbm = nullptr;
+                rc = scratch(SLOT_BITMAP, (size_t)grid * smem, &gbm);
+                if (!rc)
+                    bitmap_numeric_kernel<false><<<grid, BM_THREADS, 0, st>>>(
+                        p->n2, p->list2, p->words, (uint32_t *)gbm, p->apos, p->acrd, p->aval, p->bpos,
+                        p->bcrd32, p->bval, p->mpos, p->mcrd, p->pair, p->bm_store, p->cpos, ccrd, cval);
+            }
+            if (!rc && cudaGetLastError() != cudaSuccess) rc = fail("spgemm numeric (bitmap) launch failed");
+        }
+    }
+    if (!keep) plan_free(p, st);
+    return rc;
+}
+
+void destroy_plan(int64_t handle)
+{
+    Plan *p = find_plan(handle, true);
+    if (p) plan_free(p, nullptr);
+}
+
+}  // namespace cb200
+
+extern "C" {
+
+int32_t comet_b200_dev_spgemm_symbolic_f64_i64(int64_t nrows, int64_t ncols_b, int64_t nnz_b,
+                                               const int64_t *apos, const int64_t *acrd,
+                                               const double *aval, const int64_t *bpos,
+                                               const int64_t *bcrd, const double *bval,
+                                               const int64_t *mpos, const int64_t *mcrd,
+                                               int32_t semiring, int64_t *cpos, int64_t *nnz_host,
+                                               int64_t *handle_out, void *stream)
+{
+    cb200::clear_error();
+    if (semiring != COMET_B200_PLUS_TIMES && semiring != COMET_B200_PLUS_PAIR)
+        return cb200::fail("spgemm: unsupported semiring %d", semiring);
+    return cb200::spgemm_symbolic(nrows, ncols_b, nnz_b, apos, acrd, aval, bpos, bcrd, bval, mpos, mcrd,
+                                  semiring, cpos, nnz_host, handle_out, (cudaStream_t)stream);
+}
+
+int32_t comet_b200_dev_elews_mul_sparse_sparse_symbolic_f64_i64(
+    int64_t nrows, const int64_t *apos, const int64_t *acrd, const double *aval,
+    const int64_t *bpos, const int64_t *bcrd, const double *bval, int64_t *cpos, int64_t *nnz_host,
+    int64_t *handle_out, void *stream)
+{
+    cb200::clear_error();
+    return cb200::elews_ss_symbolic(nrows, apos, acrd, aval, bpos, bcrd, bval, cpos, nnz_host,
+                                    handle_out, (cudaStream_t)stream);
+}
+
+int32_t comet_b200_dev_spgemm_numeric_f64_i64(int64_t handle, int64_t *ccrd, double *cval,
+                                              int32_t keep, void *stream)
+{
+    cb200::clear_error();
+    return cb200::sparse_out_numeric(handle, ccrd, cval, keep, (cudaStream_t)stream);
+}
+
+void comet_b200_handle_destroy(int64_t handle) { cb200::destroy_plan(handle); }
+
+}

@@ -1,0 +1,148 @@
+// SpMV  y[a] = y[a] (+) sum_b A[a,b] (x) x[b]   (CSR / DCSR rows, f64 values, i64 indices).
+//
+// One launch, no scratch memory.  A group of T lanes (T chosen from the mean
+// row length) walks one row with 128-bit loads of crd and val (two entries per
+// load); rows longer than LONG_ROW entries are left to the end of the CTA,
+// where all 256 threads of the CTA walk each of them together.  Per row the
+// summation order is fixed, so results are reproducible run to run.
+//
+// Bound: HBM.  Algorithmic bytes per call = 8(n+1) + 16 nnz + 8 ncols + 8 nrows.
+#include "common.cuh"
+
+namespace cb200 {
+
+static const int SPMV_THREADS = 256;
+static const int SPMV_PASSES = 4;          // rows per lane group per CTA
+static const int64_t LONG_ROW = 2048;
+
+template <bool PAIR>
+__device__ __forceinline__ double combine(double a, double b)
+{
+    return PAIR ? 1.0 : a * b;
+}
+
+// Partial dot product of one row over entries handled by this lane; `nl` lanes
+// share the row, lane index `l`.  VEC: crd/val are 16-byte aligned arrays.
+template <bool PAIR, bool VEC>
+__device__ __forceinline__ double row_partial(const int64_t *__restrict__ crd,
+                                              const double *__restrict__ val,
+                                              const double *__restrict__ x, int64_t s, int64_t e,
+                                              int l, int nl)
+{
+    double sum0 = 0.0, sum1 = 0.0;
+    if (VEC) {
+        for (int64_t q = (s & ~(int64_t)1) + 2 * l; q < e; q += 2 * nl) {
+            if (q >= s && q + 1 < e) {
+                longlong2 c = __ldcs((const longlong2 *)(crd + q));
+                double2 v = __ldcs((const double2 *)(val + q));
+                sum0 += combine<PAIR>(v.x, PAIR ? 0.0 : __ldg(x + c.x));
+                sum1 += combine<PAIR>(v.y, PAIR ? 0.0 : __ldg(x + c.y));
+            } else {
+                if (q >= s) sum0 += combine<PAIR>(val[q], PAIR ? 0.0 : __ldg(x + crd[q]));
+                if (q + 1 < e) sum1 += combine<PAIR>(val[q + 1], PAIR ? 0.0 : __ldg(x + crd[q + 1]));
+            }
+        }
+    } else {
+        for (int64_t q = s + l; q < e; q += nl)
+            sum0 += combine<PAIR>(val[q], PAIR ? 0.0 : __ldg(x + crd[q]));
+    }
+    return sum0 + sum1;
+}
+
+template <int T, bool PAIR, bool VEC>
+__global__ void __launch_bounds__(SPMV_THREADS)
+spmv_kernel(int64_t nrows, const int64_t *__restrict__ row_ids, const int64_t *__restrict__ pos,
+            const int64_t *__restrict__ crd, const double *__restrict__ val,
+            const double *__restrict__ x, double *__restrict__ y, int accumulate)
+{
+    constexpr int GROUPS = SPMV_THREADS / T;
+    constexpr int ROWS = GROUPS * SPMV_PASSES;
+    __shared__ int64_t long_rows[ROWS];
+    __shared__ int n_long;
+    __shared__ double warp_part[SPMV_THREADS / 32];
+
+    const int g = threadIdx.x / T, l = threadIdx.x % T;
+    const int lane = threadIdx.x & 31;
+    const unsigned gmask = (T == 32) ? 0xffffffffu : (((1u << T) - 1u) << (lane & ~(T - 1)));
+    if (threadIdx.x == 0) n_long = 0;
+    __syncthreads();
+
+    const int64_t row0 = (int64_t)blockIdx.x * ROWS;
+    for (int pass = 0; pass < SPMV_PASSES; pass++) {
+        int64_t r = row0 + pass * GROUPS + g;
+        if (r >= nrows) break;
+        int64_t s = pos[r], e = pos[r + 1];
+        if (e - s > LONG_ROW) {
+            if (l == 0) long_rows[atomicAdd(&n_long, 1)] = r;
+            continue;
+        }
+        double sum = row_partial<PAIR, VEC>(crd, val, x, s, e, l, T);
+#pragma unroll
+        for (int o = T / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(gmask, sum, o, T);
+        if (l == 0) {
+            int64_t out = row_ids ? row_ids[r] : r;
+            y[out] = accumulate ? y[out] + sum : sum;
+        }
+    }
+    __syncthreads();
+    const int nl = n_long;
+    for (int i = 0; i < nl; i++) {
+        int64_t r = long_rows[i];
+        double sum = row_partial<PAIR, VEC>(crd, val, x, pos[r], pos[r + 1], threadIdx.x, SPMV_THREADS);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) warp_part[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int w = 0; w < SPMV_THREADS / 32; w++) t += warp_part[w];
+            int64_t out = row_ids ? row_ids[r] : r;
+            y[out] = accumulate ? y[out] + t : t;
+        }
+        __syncthreads();
+    }
+}
+
+template <int T>
+static int launch_spmv(int64_t nrows, const int64_t *row_ids, const int64_t *pos, const int64_t *crd,
+                       const double *val, const double *x, double *y, bool pair, bool vec,
+                       int accumulate, cudaStream_t st)
+{
+    constexpr int ROWS = (SPMV_THREADS / T) * SPMV_PASSES;
+    unsigned grid = (unsigned)ceil_div(nrows, ROWS);
+#define GO(P, V) spmv_kernel<T, P, V><<<grid, SPMV_THREADS, 0, st>>>(nrows, row_ids, pos, crd, val, x, y, accumulate)
+    if (pair) { if (vec) GO(true, true); else GO(true, false); }
+    else      { if (vec) GO(false, true); else GO(false, false); }
+#undef GO
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+int spmv_rows(int64_t nrows, int64_t nnz, const int64_t *row_ids, const int64_t *pos,
+              const int64_t *crd, const double *val, const double *x, double *y, int semiring,
+              int accumulate, cudaStream_t st)
+{
+    if (nrows <= 0) return 0;
+    bool vec = (((uintptr_t)crd | (uintptr_t)val) & 15) == 0;
+    bool pair = semiring == COMET_B200_PLUS_PAIR;
+    double mean = (double)nnz / (double)nrows;
+    if (mean <= 4.0) return launch_spmv<2>(nrows, row_ids, pos, crd, val, x, y, pair, vec, accumulate, st);
+    if (mean <= 8.0) return launch_spmv<4>(nrows, row_ids, pos, crd, val, x, y, pair, vec, accumulate, st);
+    if (mean <= 24.0) return launch_spmv<8>(nrows, row_ids, pos, crd, val, x, y, pair, vec, accumulate, st);
+    if (mean <= 48.0) return launch_spmv<16>(nrows, row_ids, pos, crd, val, x, y, pair, vec, accumulate, st);
+    return launch_spmv<32>(nrows, row_ids, pos, crd, val, x, y, pair, vec, accumulate, st);
+}
+
+}  // namespace cb200
+
+extern "C" int32_t comet_b200_dev_spmv_f64_i64(int64_t nrows, int64_t nnz, const int64_t *row_ids,
+                                               const int64_t *pos, const int64_t *crd,
+                                               const double *val, const double *x, double *y,
+                                               int32_t semiring, int32_t accumulate, void *stream)
+{
+    cb200::clear_error();
+    if (semiring != COMET_B200_PLUS_TIMES && semiring != COMET_B200_PLUS_PAIR)
+        return cb200::fail("spmv: unsupported semiring %d", semiring);
+    return cb200::spmv_rows(nrows, nnz, row_ids, pos, crd, val, x, y, semiring, accumulate,
+                            (cudaStream_t)stream);
+}

@@ -1,0 +1,271 @@
+/*
+ * libcomet_b200 -- C ABI of the B200 execution path for COMET's sparse
+ * tensor-algebra operations (ta.mul / ta.elews_mul on CSR, DCSR and COO
+ * operands, semirings plus-times and plus-pair, f64 values, i64 indices).
+ *
+ * Two layers, both plain C (pointers, sizes, no C++ or torch types):
+ *
+ *  1. comet_b200_<op>_f64_i64(...)      HOST memref descriptors.  These are the
+ *     symbols a COMET lowering emits func.call's to, next to read_input_2D_f64_i64
+ *     and comet_sort64.  Argument conventions follow COMET's existing runtime
+ *     calls (paths below are relative to the COMET source tree):
+ *       - a memref<?xT> crosses the boundary as (int64 rank, void *desc) where
+ *         desc points to {T *allocated; T *aligned; int64 offset; int64 sizes[rank];
+ *         int64 strides[rank]}   (lib/ExecutionEngine/SparseUtils.cpp:1829-1837,
+ *         :2622-2626; frontends/numpy-scipy/cometpy/MLIRGen/utils.py:5-21);
+ *       - a sparse tensor is passed as four format integers followed by, per
+ *         dimension, pos, crd, tile_pos, tile_crd, and finally vals, exactly as
+ *         transpose_2D_f64_i64 receives its operands
+ *         (lib/Conversion/TensorAlgebraToSCF/TensorAlgebraToSCF.cpp:303-400,
+ *          lib/ExecutionEngine/TransposeUtils.cpp:1439-1451), then a
+ *         memref<2xindex> holding {rows, cols} (same file :339-343);
+ *       - format integers use the runtime encoding Dense=0, Compressed_unique=1,
+ *         Compressed_nonunique=2, singleton=3, unknown=-1
+ *         (include/comet/ExecutionEngine/RunnerUtils.h:71-77): CSR = (0,1),
+ *         DCSR = (1,1), COO = (2,3);
+ *       - the caller allocates every output; functions return void and results
+ *         are complete in host memory on return, so comet_print_memref_* and
+ *         ta.reduce code that follows keeps working;
+ *       - symbol names follow <op>_f<valbits>_i<idxbits>
+ *         (TensorAlgebraToSCF.cpp:360, TensorDeclLowering.cpp:1038).
+ *     Tile arrays are accepted and ignored (always empty for CSR/DCSR/COO).
+ *
+ *  2. comet_b200_dev_<op>_f64_i64(...)  DEVICE pointers + sizes + a CUDA stream,
+ *     asynchronous, returning 0 or an error status.  Layer 1 is a thin wrapper
+ *     that stages host memrefs into device memory and calls layer 2.
+ *
+ * There is no CPU fallback: every entry point needs a CUDA device and fails
+ * (message on stderr, then exit(1), like COMET's runtime; or a retrievable
+ * error with COMET_B200_ON_ERROR=return) when none is usable.
+ */
+#ifndef COMET_B200_H
+#define COMET_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define COMET_B200_EXPORT __attribute__((visibility("default")))
+#else
+#define COMET_B200_EXPORT
+#endif
+
+/* semiring of ta.mul: "plusxy_times" / "plusxy_pairxy"
+   (frontends/comet_dsl/mlir/MLIRGen.cpp:102-145; arithmetic in
+   lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:198-361) */
+#define COMET_B200_PLUS_TIMES 0
+#define COMET_B200_PLUS_PAIR 1
+
+/* MaskType of ta.mul (include/comet/Dialect/TensorAlgebra/IR/TAOps.td:348-433) */
+#define COMET_B200_MASK_NONE 0
+#define COMET_B200_MASK_PUSH 1
+
+/* runtime format codes (include/comet/ExecutionEngine/RunnerUtils.h:71-77) */
+#define COMET_B200_FMT_DENSE 0
+#define COMET_B200_FMT_CU 1
+#define COMET_B200_FMT_CN 2
+#define COMET_B200_FMT_S 3
+
+/* StridedMemRefType<T,1> and <T,2> of MLIR's C runner ABI, restated. */
+typedef struct {
+    void *allocated;
+    void *aligned;
+    int64_t offset;
+    int64_t sizes[1];
+    int64_t strides[1];
+} comet_b200_memref1d;
+
+typedef struct {
+    void *allocated;
+    void *aligned;
+    int64_t offset;
+    int64_t sizes[2];
+    int64_t strides[2];
+} comet_b200_memref2d;
+
+/* One sparse 2-D operand, in the order COMET passes it to its runtime. */
+#define COMET_B200_SPARSE2D(P)                                                          \
+    int32_t P##1format, int32_t P##1tile_format, int32_t P##2format, int32_t P##2tile_format, \
+        int64_t P##1pos_rank, void *P##1pos_ptr, int64_t P##1crd_rank, void *P##1crd_ptr,     \
+        int64_t P##1tile_pos_rank, void *P##1tile_pos_ptr, int64_t P##1tile_crd_rank,         \
+        void *P##1tile_crd_ptr, int64_t P##2pos_rank, void *P##2pos_ptr, int64_t P##2crd_rank, \
+        void *P##2crd_ptr, int64_t P##2tile_pos_rank, void *P##2tile_pos_ptr,                 \
+        int64_t P##2tile_crd_rank, void *P##2tile_crd_ptr, int64_t P##val_rank, void *P##val_ptr, \
+        int64_t P##dims_rank, void *P##dims_ptr
+
+/* ------------------------------------------------------------------------- */
+/* Layer 1: host memref descriptors                                           */
+/* ------------------------------------------------------------------------- */
+
+/* `accumulate` (spmv, spmm): 1 = the dense output holds values the products are
+   added to, which is what COMET's loops do (they read-modify-write the output,
+   IndexTreeToSCF.cpp:1266-1278); 0 = the lowering has seen the ta.fill 0.0 that
+   precedes the multiply (every reference test has one), so the old contents are
+   neither uploaded nor read. */
+
+/* y[a] = y[a] (+) sum_b A[a,b] (x) x[b].  Replaces the loop nest COMET generates
+   for ta.mul with a CSR/DCSR/COO lhs and a dense vector
+   (lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:476-489, 667-783, 1247-1284;
+   test/integration/ops/mult_spmv_{CSR,DCSR,COO}xDense.ta). */
+COMET_B200_EXPORT void comet_b200_spmv_f64_i64(COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr,
+                                               int64_t y_rank, void *y_ptr, int32_t semiring,
+                                               int32_t accumulate);
+
+/* C[a,c] = C[a,c] (+) sum_b A[a,b] (x) B[b,c], B and C row-major 2-D memrefs.
+   Replaces the a->b->c loop nest of ta.mul sparse x dense
+   (TensorAlgebraToIndexTree.cpp:276-323; test/integration/ops/mult_spmm_*xDense.ta). */
+COMET_B200_EXPORT void comet_b200_spmm_f64_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                                               int64_t C_rank, void *C_ptr, int32_t semiring,
+                                               int32_t accumulate);
+
+/* O = S .* (X * D): O takes S's pos/crd, O.val[p] = S.val[p] * sum_k X[i,k] * D[k,j].
+   X is a row-major [rows, K] memref; D is a 2-D memref of sizes {K, cols} whose
+   strides select the layout: {ld, 1} is the D[k,j] operand of
+   test/integration/kernels/sddmm.ta, {1, ld} is a row-major [cols, K] matrix
+   viewed transposed.  Replaces the ta.mul + ta.elews_mul pair that COMET fuses
+   with --opt-fusion (lib/Dialect/IndexTree/Transforms/KernelFusion.cpp:127-144). */
+COMET_B200_EXPORT void comet_b200_sddmm_f64_i64(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr,
+                                                int64_t D_rank, void *D_ptr,
+                                                COMET_B200_SPARSE2D(O));
+
+/* C = A .* B with sparse A (CSR or COO) and dense row-major B; C takes A's
+   pos/crd (lib/Conversion/IndexTreeToSCF/SymbolicDomainConversion.cpp:277-297;
+   test/integration/ops/eltwise_mult_{CSR,COO}xDense_o{CSR,COO}.ta). */
+COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_f64_i64(COMET_B200_SPARSE2D(A),
+                                                                 int64_t B_rank, void *B_ptr,
+                                                                 COMET_B200_SPARSE2D(C));
+
+/* Sparse-output operations use the two-call protocol COMET already uses for
+   file input (read_input_sizes_2D_f64 then read_input_2D_f64_i64,
+   lib/Dialect/TensorAlgebra/Transforms/TensorDeclLowering.cpp:937-1052): the
+   symbolic call fills C2pos[rows+1] and an 11-entry sizes array laid out like
+   read_input_sizes_2D's (SparseUtils.cpp:1672-1687) and returns a handle; the
+   caller allocates C2crd[nnz], Cval[nnz]; the numeric call fills them and
+   releases the handle.  Output A1pos = {rows}, A1crd unused
+   (SymbolicDomainConversion.cpp:262-271). */
+
+/* C = A*B or C<M,push> = A*B, all CSR, Gustavson row by row.  Restates the
+   workspace transformation and its symbolic phase
+   (lib/Dialect/IndexTree/Transforms/WorkspaceTransforms.cpp:97-276,
+    lib/Conversion/IndexTreeToSCF/SymbolicDomainConversion.cpp:81-340,
+    lib/Conversion/TensorAlgebraToSCF/SparseTensorConversionPass.cpp:982-1159);
+   output crd sorted per row like comet_sort64 leaves it.  Pass mask_type
+   COMET_B200_MASK_NONE and any (ignored) M block when there is no mask.  The
+   mask's crd must be ascending within a row. */
+COMET_B200_EXPORT int64_t comet_b200_spgemm_symbolic_f64_i64(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr);
+
+COMET_B200_EXPORT void comet_b200_spgemm_numeric_f64_i64(int64_t handle, int64_t C2crd_rank,
+                                                         void *C2crd_ptr, int64_t Cval_rank,
+                                                         void *Cval_ptr);
+
+/* C = A .* B, both CSR: per-row intersection
+   (lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:854-1073;
+   test/integration/ops/eltwise_mult_CSRxCSR_oCSR.ta).  Same protocol; finish
+   with comet_b200_spgemm_numeric_f64_i64. */
+COMET_B200_EXPORT int64_t comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), int64_t C2pos_rank, void *C2pos_ptr,
+    int64_t sizes_rank, void *sizes_ptr);
+
+/* Drops a handle without running the numeric phase. */
+COMET_B200_EXPORT void comet_b200_handle_destroy(int64_t handle);
+
+/* out[0] = SUM(C<M,push> = A*B) under plus-pair, as an exact int64, without
+   storing C: the fused form of the masked ta.mul + ta.reduce of
+   test/integration/kernels/triangleCount_SandiaLL_wMasking.ta
+   (mask: lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:1075-1162, 1327-1448;
+    reduce: lib/Conversion/TensorAlgebraToSCF/TensorAlgebraToSCF.cpp:417-529).
+   With A = B = M = L (strict lower triangle) this is the triangle count. */
+COMET_B200_EXPORT void comet_b200_masked_spgemm_count_f64_i64(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t out_rank, void *out_ptr);
+
+/* ------------------------------------------------------------------------- */
+/* Error reporting (COMET's runtime has none beyond stderr + exit; see         */
+/* SparseUtils.cpp:158-168).                                                   */
+/* ------------------------------------------------------------------------- */
+COMET_B200_EXPORT const char *comet_b200_last_error(void);   /* "" when the last call succeeded */
+COMET_B200_EXPORT void comet_b200_set_error_mode(int32_t return_instead_of_exit);
+COMET_B200_EXPORT int32_t comet_b200_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Layer 2: device pointers.  All arrays live in the current device's memory; */
+/* `stream` is a cudaStream_t (NULL = default stream).  row_ids, when not      */
+/* NULL, maps stored row r to its coordinate (the A1crd array of DCSR) and     */
+/* nrows is then the number of stored rows.  Returns 0 on success.             */
+/* ------------------------------------------------------------------------- */
+COMET_B200_EXPORT int32_t comet_b200_dev_spmv_f64_i64(int64_t nrows, int64_t nnz,
+                                                      const int64_t *row_ids,
+                                                      const int64_t *pos, const int64_t *crd,
+                                                      const double *val, const double *x, double *y,
+                                                      int32_t semiring, int32_t accumulate,
+                                                      void *stream);
+
+/* variant: 0 = automatic; otherwise (panel width in columns) | (lanes per row << 16),
+   the number of B columns handled per pass over A and the lane-group size, for tuning. */
+COMET_B200_EXPORT int32_t comet_b200_dev_spmm_f64_i64(int64_t nrows, int64_t ncols, int64_t nnz,
+                                                      int64_t k,
+                                                      const int64_t *row_ids, const int64_t *pos,
+                                                      const int64_t *crd, const double *val,
+                                                      const double *b, int64_t ldb, double *c,
+                                                      int64_t ldc, int32_t semiring,
+                                                      int32_t accumulate, int32_t variant,
+                                                      void *stream);
+
+/* y is row-major [ncols, k] with leading dimension ldy. */
+COMET_B200_EXPORT int32_t comet_b200_dev_sddmm_f64_i64(int64_t nrows, int64_t nnz, int64_t k,
+                                                       const int64_t *pos,
+                                                       const int64_t *crd, const double *sval,
+                                                       const double *x, int64_t ldx, const double *y,
+                                                       int64_t ldy, double *out, void *stream);
+
+/* dst[j, i] = src[i, j] for a row-major [rows, cols] src (used to bring a D[k,j]
+   operand into the [cols, K] layout the SDDMM kernel gathers from). */
+COMET_B200_EXPORT int32_t comet_b200_dev_transpose_f64(int64_t rows, int64_t cols, const double *src,
+                                                       int64_t lds, double *dst, int64_t ldd,
+                                                       void *stream);
+
+/* rows == NULL: CSR (pos given); rows != NULL: COO (row coordinate per entry). */
+COMET_B200_EXPORT int32_t comet_b200_dev_elews_mul_sparse_dense_f64_i64(
+    int64_t nrows, int64_t nnz, const int64_t *pos, const int64_t *rows, const int64_t *crd,
+    const double *val, const double *b, int64_t ldb, double *out, void *stream);
+
+/* Sparse-output operations on device arrays.  *handle_out receives a handle,
+   cpos[nrows+1] is filled, *nnz_host (host memory) receives nnz(C) after an
+   internal stream synchronisation (the caller has to size crd/val). */
+COMET_B200_EXPORT int32_t comet_b200_dev_spgemm_symbolic_f64_i64(
+    int64_t nrows, int64_t ncols_b, int64_t nnz_b, const int64_t *apos, const int64_t *acrd,
+    const double *aval, const int64_t *bpos, const int64_t *bcrd, const double *bval,
+    const int64_t *mpos, const int64_t *mcrd, int32_t semiring, int64_t *cpos, int64_t *nnz_host,
+    int64_t *handle_out, void *stream);
+
+COMET_B200_EXPORT int32_t comet_b200_dev_elews_mul_sparse_sparse_symbolic_f64_i64(
+    int64_t nrows, const int64_t *apos, const int64_t *acrd, const double *aval,
+    const int64_t *bpos, const int64_t *bcrd, const double *bval, int64_t *cpos, int64_t *nnz_host,
+    int64_t *handle_out, void *stream);
+
+/* The operand arrays given to the symbolic call must still be valid.  keep != 0
+   leaves the handle alive so the numeric phase can be repeated (benchmarks). */
+COMET_B200_EXPORT int32_t comet_b200_dev_spgemm_numeric_f64_i64(int64_t handle, int64_t *ccrd,
+                                                                double *cval, int32_t keep,
+                                                                void *stream);
+
+/* *count_dev (device memory, int64) receives the number of products A[i,k]*B[k,j]
+   with (i,j) stored in M, over rows [row_lo, row_hi) of A and M.  Rows of B and M
+   must hold strictly ascending column coordinates (no duplicates). */
+COMET_B200_EXPORT int32_t comet_b200_dev_masked_spgemm_count_f64_i64(
+    int64_t row_lo, int64_t row_hi, int64_t ncols, int64_t nnz_a, int64_t nnz_b, int64_t nnz_m,
+    const int64_t *apos, const int64_t *acrd, const int64_t *bpos, const int64_t *bcrd,
+    const int64_t *mpos, const int64_t *mcrd, int64_t *count_dev, void *stream);
+
+/* Frees the library's scratch memory on the current device. */
+COMET_B200_EXPORT void comet_b200_release_scratch(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COMET_B200_H */

@@ -1,0 +1,62 @@
+"""CPU checks of the boundary: the shared library loads and exports every symbol
+that include/comet_b200.h declares, and fails loudly instead of falling back
+when no CUDA device is present."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "comet_b200.h")).read()
+    return sorted(set(re.findall(r"\b(comet_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_expected_entry_points():
+    names = _declared()
+    for want in ("comet_b200_spmv_f64_i64", "comet_b200_spmm_f64_i64", "comet_b200_sddmm_f64_i64",
+                 "comet_b200_spgemm_symbolic_f64_i64", "comet_b200_spgemm_numeric_f64_i64",
+                 "comet_b200_masked_spgemm_count_f64_i64", "comet_b200_dev_spmm_f64_i64"):
+        assert want in names
+
+
+def test_library_exports_every_declared_symbol():
+    from comet_b200 import _lib, build
+    build.build_library()
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    missing = [n for n in _declared() if not hasattr(lib, n)]
+    assert not missing, missing
+    # and the ctypes table covers the same set
+    assert sorted(_lib.SIGNATURES) == _declared()
+
+
+def test_no_cpu_fallback_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    import scipy.sparse as sp
+    import comet_b200
+    from comet_b200._lib import CometB200Error
+    A = sp.random(8, 8, density=0.3, format="csr", random_state=0)
+    with pytest.raises(CometB200Error, match="no CUDA device|CUDA"):
+        comet_b200.spmv(A, np.ones(8))
+
+
+def test_bad_descriptors_are_rejected_on_the_host():
+    import comet_b200
+    from comet_b200._lib import CometB200Error
+    from comet_b200.api import SparseTensor
+    bad = SparseTensor("CSR", 4, 4, np.array([4]), np.array([-1]), np.array([0, 1, 2]),  # pos too short
+                       np.array([0, 1]), np.array([1.0, 2.0]))
+    with pytest.raises(CometB200Error, match="pos array shorter"):
+        comet_b200.spmv(bad, np.ones(4))
+    ok = SparseTensor("CSR", 2, 2, np.array([2]), np.array([-1]), np.array([0, 1, 2]), np.array([0, 1]),
+                      np.array([1.0, 2.0]))
+    with pytest.raises(CometB200Error, match="x shorter"):
+        comet_b200.spmv(ok, np.ones(1))
+    with pytest.raises(ValueError, match="semiring"):
+        comet_b200.spmv(ok, np.ones(2), semiring="min,plus")

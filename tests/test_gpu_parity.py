@@ -1,0 +1,232 @@
+"""Parity of the CUDA path with the CPU oracle on seeded inputs: structure
+(pos, crd) and integer results bit-exact, float64 values within 1e-12 relative
+(the tolerance the path is specified to; differences come from summation order).
+
+For sums of signed terms the error of any summation order is bounded by
+eps * n * sum(|terms|), so values are compared relative to max(|ref|, sum(|terms|)):
+an entry that cancels to nearly zero is not held to 1e-12 of its tiny result."""
+import numpy as np
+import pytest
+import scipy.sparse as sp
+import torch
+
+import comet_b200.api as api
+import comet_b200.device as dev
+from comet_b200 import datasets
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-12
+
+
+def _orc(t):
+    return oracle.SparseArrays(t.format, t.nrows, t.ncols, t.a1pos, t.a1crd, t.a2pos, t.a2crd, t.val)
+
+
+def _abs(t):
+    return oracle.SparseArrays(t.format, t.nrows, t.ncols, t.a1pos, t.a1crd, t.a2pos, t.a2crd, np.abs(t.val))
+
+
+def _close(got, ref, scale):
+    got, ref, scale = np.asarray(got), np.asarray(ref), np.asarray(scale)
+    assert got.shape == ref.shape
+    err = np.abs(got - ref)
+    bound = RTOL * np.maximum(np.abs(ref), scale)
+    bad = err > bound
+    assert not bad.any(), "max rel err %.3e at %d entries" % (float((err / np.maximum(bound, 1e-300)).max() * RTOL), int(bad.sum()))
+
+
+def _skewed(n=3000, seed=0):
+    """CSR with empty rows, short rows, and a few rows far longer than any lane group or chunk."""
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(0, 12, n)
+    lens[rng.integers(0, n, n // 5)] = 0
+    lens[[1, n // 2, n - 1]] = [2500, 700, 1301]
+    rows = np.repeat(np.arange(n), lens)
+    cols = np.concatenate([np.sort(rng.choice(n, l, replace=False)) for l in lens])
+    vals = rng.uniform(-1, 1, rows.shape[0])
+    m = sp.csr_matrix((vals, (rows, cols)), shape=(n, n))
+    m.sort_indices()
+    return api.as_sparse(m)
+
+
+@pytest.mark.parametrize("make", [lambda: datasets.config_spmv(n=2048, per_row=16)[0],
+                                  lambda: datasets.rmat_csr(12, 16, seed=2), _skewed])
+def test_spmv_parity(make):
+    A = make()
+    x = datasets.dense_uniform(A.ncols, 11)
+    y0 = datasets.dense_uniform(A.nrows, 12)
+    ref = oracle.spmv(_orc(A), x, y0)
+    scale = oracle.spmv(_abs(A), np.abs(x), np.abs(y0))
+    _close(api.spmv(A, x, y0), ref, scale)
+    _close(api.spmv(A, x), oracle.spmv(_orc(A), x), scale)
+    # plus-pair: exact small integers
+    assert np.array_equal(api.spmv(A, x, semiring=api.PLUS_PAIR), oracle.spmv(_orc(A), x, semiring=oracle.PLUS_PAIR))
+
+
+@pytest.mark.parametrize("k", [128, 64, 32, 6, 5, 1])
+def test_spmm_parity(k):
+    A = _skewed(2000, seed=k)
+    B = datasets.dense_uniform((A.ncols, k), 3)
+    C0 = datasets.dense_uniform((A.nrows, k), 4)
+    ref = oracle.spmm(_orc(A), B, C0)
+    scale = oracle.spmm(_abs(A), np.abs(B), np.abs(C0))
+    _close(api.spmm(A, B, C0), ref, scale)
+    _close(api.spmm(A, B), oracle.spmm(_orc(A), B), scale)
+
+
+def test_spmm_rmat_and_panel_variants():
+    A, B = datasets.config_spmm(scale=13, edge_factor=16, k=128)
+    ref = oracle.spmm(_orc(A), B)
+    scale = oracle.spmm(_abs(A), np.abs(B))
+    dA = dev.to_device(A)
+    dB = torch.from_numpy(B).cuda()
+    for variant in (0, 64, 32, 16, 32 | (8 << 16), 128 | (16 << 16)):
+        C = dev.spmm(dA, dB, variant=variant)
+        _close(C.cpu().numpy(), ref, scale)
+    # plus-pair counts entries per row in every column
+    Cp = dev.spmm(dA, dB, semiring=api.PLUS_PAIR).cpu().numpy()
+    assert np.array_equal(Cp, np.repeat(np.diff(A.a2pos)[:, None], 128, axis=1).astype(np.float64))
+
+
+@pytest.mark.parametrize("fmt", ["DCSR", "COO"])
+def test_dcsr_and_coo_operands(fmt, tmp_path):
+    A = _skewed(500, seed=9)
+    path = tmp_path / "a.mtx"
+    datasets.write_mtx(str(path), A)
+    T = oracle.read_mtx(str(path), fmt)
+    x = datasets.dense_uniform(A.ncols, 1)
+    B = datasets.dense_uniform((A.ncols, 8), 2)
+    y0 = datasets.dense_uniform(A.nrows, 5)
+    _close(api.spmv(T, x, y0), oracle.spmv(T, x, y0), oracle.spmv(_abs(T), np.abs(x), np.abs(y0)))
+    _close(api.spmm(T, B), oracle.spmm(T, B), oracle.spmm(_abs(T), np.abs(B)))
+
+
+def test_unsorted_coo_is_rejected():
+    from comet_b200._lib import CometB200Error
+    m = sp.coo_matrix((np.ones(3), (np.array([2, 0, 1]), np.array([0, 1, 2]))), shape=(3, 3))
+    with pytest.raises(CometB200Error, match="ascending"):
+        api.spmv(m, np.ones(3))
+
+
+@pytest.mark.parametrize("k", [64, 128, 16, 10, 7])
+def test_sddmm_parity(k):
+    S = _skewed(1500, seed=k)
+    X = datasets.dense_uniform((S.nrows, k), 1)
+    Y = datasets.dense_uniform((S.ncols, k), 2)
+    ref = oracle.sddmm(_orc(S), X, Y)
+    scale = oracle.sddmm(_abs(S), np.abs(X), np.abs(Y))
+    _close(api.sddmm(S, X, Y), ref, scale)
+    # the D[k, j] operand layout of the reference's sddmm.ta
+    _close(api.sddmm(S, X, np.ascontiguousarray(Y.T), y_is_kj=True), ref, scale)
+
+
+def test_sddmm_rmat():
+    S, X, Y = datasets.config_sddmm(scale=12, edge_factor=32, k=64)
+    _close(api.sddmm(S, X, Y), oracle.sddmm(_orc(S), X, Y), oracle.sddmm(_abs(S), np.abs(X), np.abs(Y)))
+
+
+def test_elementwise():
+    A = _skewed(800, seed=4)
+    B = datasets.dense_uniform((A.nrows, A.ncols), 6)
+    assert np.array_equal(api.elews_sparse_dense(A, B), oracle.elews_sparse_dense(_orc(A), B))
+    A2 = _skewed(800, seed=5)
+    got, ref = api.elews_csr_csr(A, A2), oracle.elews_csr_csr(_orc(A), _orc(A2))
+    assert np.array_equal(got.a2pos, ref.a2pos) and np.array_equal(got.a2crd, ref.a2crd)
+    assert np.array_equal(got.val, ref.val)
+
+
+def _check_spgemm(A, B, M=None, semiring=api.PLUS_TIMES):
+    got = api.spgemm(A, B, M, semiring)
+    ref = oracle.spgemm(_orc(A), _orc(B), _orc(M) if M is not None else None, semiring)
+    assert np.array_equal(got.a2pos, ref.a2pos)
+    assert np.array_equal(got.a2crd, ref.a2crd)
+    if semiring == api.PLUS_PAIR:
+        assert np.array_equal(got.val, ref.val)
+    else:
+        scale = oracle.spgemm(_abs(A), _abs(B), _orc(M) if M is not None else None, semiring).val
+        _close(got.val, ref.val, scale)
+    return got
+
+
+@pytest.mark.parametrize("scale,ef", [(8, 4), (11, 8), (13, 16)])
+def test_spgemm_rmat_parity(scale, ef):
+    A = datasets.config_spgemm(scale=scale, edge_factor=ef)
+    C = _check_spgemm(A, A)
+    assert C.nnz > 0
+    _check_spgemm(A, A, semiring=api.PLUS_PAIR)
+
+
+def test_spgemm_rectangular_empty_and_long_rows():
+    rng = np.random.default_rng(0)
+    A = sp.random(300, 5000, density=0.02, random_state=rng, format="csr")
+    B = sp.random(5000, 70000, density=0.002, random_state=rng, format="csr")   # rows of C far beyond the hash bin
+    A.sort_indices(); B.sort_indices()
+    A, B = api.as_sparse(A), api.as_sparse(B)
+    A.val[:] = rng.uniform(-1, 1, A.nnz)
+    _check_spgemm(A, B)
+    Z = api.as_sparse(sp.csr_matrix((300, 5000)))
+    got = api.spgemm(Z, B)
+    assert got.nnz == 0 and np.all(got.a2pos == 0)
+
+
+def test_spgemm_many_columns_uses_global_bitmaps():
+    rng = np.random.default_rng(1)
+    n = 1_200_000                                    # bitmap + ranks no longer fit shared memory
+    A = sp.random(64, 2000, density=0.2, random_state=rng, format="csr")
+    B = sp.random(2000, n, density=2e-4, random_state=rng, format="csr")
+    A.sort_indices(); B.sort_indices()
+    _check_spgemm(api.as_sparse(A), api.as_sparse(B))
+
+
+@pytest.mark.parametrize("scale", [9, 12])
+def test_masked_spgemm_and_triangle_count(scale):
+    L = datasets.config_triangles(scale=scale, edge_factor=8)
+    C = _check_spgemm(L, L, L, api.PLUS_PAIR)
+    want = oracle.masked_pair_count(_orc(L), _orc(L), _orc(L))
+    assert int(round(api.reduce_sum(C.val))) == want
+    assert api.triangle_count(L) == want
+    # cross-check with scipy on the smaller case
+    if scale == 9:
+        m = L.to_scipy()
+        assert want == int((m @ m).multiply(m).sum())
+    # masked plus-times, mask different from the operands
+    A = datasets.rmat_csr(scale, 8, seed=5)
+    M = datasets.rmat_csr(scale, 16, seed=6)
+    _check_spgemm(A, A, M)
+    assert api.masked_pair_count(A, A, M) == oracle.masked_pair_count(_orc(A), _orc(A), _orc(M))
+
+
+def test_device_layer_row_ranges_and_repeat_calls():
+    L = datasets.config_triangles(scale=11, edge_factor=8)
+    dL = dev.to_device(L)
+    ol = _orc(L)
+    half = L.nrows // 3
+    a = int(dev.masked_pair_count(dL, dL, dL, 0, half).item())
+    b = int(dev.masked_pair_count(dL, dL, dL, half, L.nrows).item())
+    assert a == oracle.masked_pair_count(ol, ol, ol, 0, half)
+    assert a + b == oracle.masked_pair_count(ol, ol, ol)
+    # numeric phase repeated on a kept handle gives the same structure
+    A = datasets.config_spgemm(scale=10, edge_factor=8)
+    dA = dev.to_device(A)
+    h, cpos, nnz = dev.spgemm_symbolic(dA, dA)
+    crd1, val1 = dev.spgemm_numeric(h, nnz, "cuda", keep=True)
+    crd2, val2 = dev.spgemm_numeric(h, nnz, "cuda", keep=False)
+    assert torch.equal(crd1, crd2)
+    ref = oracle.spgemm(_orc(A), _orc(A))
+    assert np.array_equal(cpos.cpu().numpy(), ref.a2pos) and np.array_equal(crd1.cpu().numpy(), ref.a2crd)
+    _close(val2.cpu().numpy(), ref.val, ref.val)
+
+
+def test_einsum_surface_matches_cometpy_forms():
+    A = datasets.rmat_csr(9, 8, seed=1).to_scipy()
+    x = datasets.dense_uniform(A.shape[1], 2)
+    B = datasets.dense_uniform((A.shape[1], 4), 3)
+    np.testing.assert_allclose(api.einsum("ij,j->i", A, x), A @ x, rtol=1e-12, atol=1e-13)
+    np.testing.assert_allclose(api.einsum("ij,jk->ik", A, B), A @ B, rtol=1e-12, atol=1e-13)
+    C = api.einsum("ij,jk->ik", A, A, mask=A, mask_type="push", semiring="+,pair")
+    want = (A.astype(bool).astype(float) @ A.astype(bool).astype(float)).multiply(A.astype(bool)).tocsr()
+    want.sort_indices(); want.eliminate_zeros()
+    got = C.to_scipy(); got.eliminate_zeros()
+    assert (abs(got - want)).nnz == 0
