@@ -42,7 +42,7 @@ def _skewed(n=3000, seed=0):
     rng = np.random.default_rng(seed)
     lens = rng.integers(0, 12, n)
     lens[rng.integers(0, n, n // 5)] = 0
-    lens[[1, n // 2, n - 1]] = [2500, 700, 1301]
+    lens[[1, n // 2, n - 1]] = [min(2500, n - 7), min(700, n // 2), min(1301, n // 3)]
     rows = np.repeat(np.arange(n), lens)
     cols = np.concatenate([np.sort(rng.choice(n, l, replace=False)) for l in lens])
     vals = rng.uniform(-1, 1, rows.shape[0])
