@@ -43,6 +43,8 @@ SIGNATURES = {
     "comet_b200_dev_spmv_f64_i64": (c_int32, [c_int64, c_int64] + [c_void_p] * 6 + [c_int32, c_int32, c_void_p]),
     "comet_b200_dev_spmm_f64_i64": (c_int32, [c_int64] * 4 + [c_void_p] * 5 + [c_int64, c_void_p, c_int64,
                                               c_int32, c_int32, c_int32, c_void_p]),
+    "comet_b200_dev_spmm_noalloc_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 5 + [c_int64, c_void_p, c_int64,
+                                                      c_int32, c_int32, c_void_p]),
     "comet_b200_dev_sddmm_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 4 + [c_int64, c_void_p, c_int64,
                                                c_void_p, c_void_p]),
     "comet_b200_dev_transpose_f64": (c_int32, [c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),

@@ -327,3 +327,102 @@ extern "C" int32_t comet_b200_dev_spmm_f64_i64(int64_t nrows, int64_t ncols, int
     return cb200::spmm_rows(nrows, ncols, nnz, k, row_ids, pos, crd, val, b, ldb, c, ldc, semiring,
                             accumulate, variant, (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------
+// SpMM for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot tolerate a cudaMalloc inside the call: a
+// COMET-generated program that runs with a fixed memory budget handed out at
+// start-up, a serving loop that forbids anything that may synchronise the
+// device, or an embedding runtime that owns the whole heap.  The regular entry
+// point keeps its long-row work list in scratch memory that grows on demand;
+// this variant keeps that list in a fixed array that is part of the loaded
+// library image instead, so the call itself allocates nothing.
+//
+// The price is a size limit (the list holds NOALLOC_MAX_CHUNKS entries, which
+// bounds the number of stored entries of A) and sharing: every call on a device
+// uses the same array, which still holds the previous call's list when the next
+// one starts.  The header is therefore cleared at the start of each call, and
+// two calls that may overlap on the GPU (different streams) would corrupt each
+// other's list and must be serialised by the caller.
+// ---------------------------------------------------------------------------
+namespace cb200 {
+
+static const size_t NOALLOC_BYTES = (size_t)4 << 20;   // 4 MiB per device that loads the library
+static const size_t NOALLOC_MAX_CHUNKS = (NOALLOC_BYTES - sizeof(WorkHeader)) / sizeof(Chunk);
+
+// Device-side storage.  In host code this name only stands for the symbol; the
+// address kernels can use is obtained with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_worklist[NOALLOC_BYTES];
+
+static void *g_noalloc_addr[64] = {nullptr};   // per device, filled on first use
+
+static int noalloc_worklist(void **out)
+{
+    int d = 0;
+    CB_CUDA(cudaGetDevice(&d));
+    if (d < 0 || d >= 64) return fail("spmm (no-alloc): device index %d out of range", d);
+    if (!g_noalloc_addr[d]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_worklist);
+        if (e != cudaSuccess || !p)
+            return fail("spmm (no-alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_noalloc_addr[d] = p;
+    }
+    *out = g_noalloc_addr[d];
+    return 0;
+}
+
+int spmm_rows_noalloc(int64_t nrows, int64_t nnz, int64_t k, const int64_t *row_ids,
+                      const int64_t *pos, const int64_t *crd, const double *val, const double *b,
+                      int64_t ldb, double *c, int64_t ldc, int semiring, int accumulate,
+                      cudaStream_t st)
+{
+    if (nrows <= 0 || k <= 0) return 0;
+    if (nnz < 0) return fail("spmm (no-alloc): negative nnz");
+    const size_t need = (size_t)(nnz / SPMM_CHUNK + nnz / SPMM_LONG_ROW + 16);
+    if (need > NOALLOC_MAX_CHUNKS)
+        return fail("spmm (no-alloc): %lld stored entries need a work list of %zu chunks, the built-in "
+                    "list holds %zu (about %lld entries); use comet_b200_dev_spmm_f64_i64",
+                    (long long)nnz, need, NOALLOC_MAX_CHUNKS,
+                    (long long)((NOALLOC_MAX_CHUNKS - 16) * SPMM_CHUNK / 2));
+    if (k % 2 != 0 || ldb % 2 != 0 || ldc % 2 != 0 || ((((uintptr_t)b | (uintptr_t)c) & 15) != 0))
+        return fail("spmm (no-alloc): K and both leading dimensions must be even and B, C 16-byte aligned");
+    if (k > 256) return fail("spmm (no-alloc): at most 256 columns per call (got %lld)", (long long)k);
+    void *wl = nullptr;
+    CB_TRY(noalloc_worklist(&wl));
+
+    int w = (int)k;
+    int t = next_pow2((w + 1) / 2);
+    if (t > 32) t = 32;
+    if (t < 2) t = 2;
+    int ni = next_pow2((int)ceil_div(w, 2 * t));
+
+    SpmmArgs a;
+    a.nrows = nrows; a.nnz = nnz; a.row_ids = row_ids; a.pos = pos; a.crd = crd; a.val = val;
+    a.b = b; a.ldb = ldb; a.c = c; a.ldc = ldc; a.k = (int)k; a.slice_cols = w; a.nslices = 1;
+    a.accumulate = accumulate; a.pair = semiring == COMET_B200_PLUS_PAIR; a.st = st;
+    a.hdr = (WorkHeader *)wl;
+    a.chunks = (Chunk *)((char *)wl + sizeof(WorkHeader));
+    a.chunk_cap = (unsigned)NOALLOC_MAX_CHUNKS;
+    // the array keeps the previous call's list: the count has to start at zero
+    CB_CUDA(cudaMemsetAsync(a.hdr, 0, sizeof(WorkHeader), st));
+    return dispatch_panels<int64_t>(a, t, ni);
+}
+
+}  // namespace cb200
+
+extern "C" int32_t comet_b200_dev_spmm_noalloc_f64_i64(int64_t nrows, int64_t nnz, int64_t k,
+                                                       const int64_t *row_ids, const int64_t *pos,
+                                                       const int64_t *crd, const double *val,
+                                                       const double *b, int64_t ldb, double *c,
+                                                       int64_t ldc, int32_t semiring,
+                                                       int32_t accumulate, void *stream)
+{
+    cb200::clear_error();
+    if (semiring != COMET_B200_PLUS_TIMES && semiring != COMET_B200_PLUS_PAIR)
+        return cb200::fail("spmm (no-alloc): unsupported semiring %d", semiring);
+    if (ldb < k || ldc < k) return cb200::fail("spmm (no-alloc): leading dimension smaller than K");
+    return cb200::spmm_rows_noalloc(nrows, nnz, k, row_ids, pos, crd, val, b, ldb, c, ldc, semiring,
+                                    accumulate, (cudaStream_t)stream);
+}

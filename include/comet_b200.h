@@ -216,6 +216,25 @@ COMET_B200_EXPORT int32_t comet_b200_dev_spmm_f64_i64(int64_t nrows, int64_t nco
                                                       int32_t accumulate, int32_t variant,
                                                       void *stream);
 
+/* SpMM that allocates nothing (this entry point has no counterpart in the
+   reference; it exists for hosts of this library that cannot call cudaMalloc
+   inside an operation: programs running under a fixed device-memory budget,
+   latency-critical loops where an allocation could stall the device, runtimes
+   that own the whole heap).  Same operation and arguments as
+   comet_b200_dev_spmm_f64_i64 without the tuning knob; the long-row work list
+   lives in a 4 MiB array inside the library image (held by every GPU that loads
+   the library until the process exits) instead of growable scratch memory.
+   Limits: nnz up to about 67 million (the list's capacity), k <= 256 and even,
+   ldb/ldc even, b and c 16-byte aligned; anything beyond is refused with an
+   error, never truncated.  The first call on a device looks up the array's
+   device address; make that call before starting any stream capture.  All
+   calls on a device share the array, so calls that can overlap on the GPU
+   (different streams) race on it and must be serialised by the caller. */
+COMET_B200_EXPORT int32_t comet_b200_dev_spmm_noalloc_f64_i64(
+    int64_t nrows, int64_t nnz, int64_t k, const int64_t *row_ids, const int64_t *pos,
+    const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
+    int32_t semiring, int32_t accumulate, void *stream);
+
 /* y is row-major [ncols, k] with leading dimension ldy. */
 COMET_B200_EXPORT int32_t comet_b200_dev_sddmm_f64_i64(int64_t nrows, int64_t nnz, int64_t k,
                                                        const int64_t *pos,
