@@ -476,6 +476,8 @@ def main():
     ap.add_argument("--variant", type=int, default=0, help="SpMM panel width | lanes << 16 (tuning)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="device-resident timing only (no end-to-end leg, no CPU leg): for profiler runs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -539,14 +541,19 @@ def main():
     kernel_ms = k0.elapsed_time(k1) / args.steps
 
     # end to end through the host-memref entry point (pinned host buffers)
-    h2d, d2h = w.e2e_setup(block, torch)
-    w.e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.e2e_steps):
+    if args.kernel_only:
+        h2d = d2h = 0
+        e2e_s = torch.tensor([float("nan")], dtype=torch.float64, device="cuda")
+        args.no_cpu = True
+    else:
+        h2d, d2h = w.e2e_setup(block, torch)
         w.e2e_step()
-    barrier()
-    e2e_s = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], dtype=torch.float64, device="cuda")
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            w.e2e_step()
+        barrier()
+        e2e_s = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     clocks = sampler.stop()

@@ -1,12 +1,15 @@
 // SDDMM  out[p] = S.val[p] * sum_k X[i,k] * Y[j,k]   for every stored (i,j) of S (CSR).
 //
-// A group of G lanes owns one row i: it keeps its part of X[i,:] in registers
-// (2*NI doubles per lane), loads G column coordinates at a time with one
-// coalesced streaming load, and for each of them gathers Y[j,:] with 128-bit
-// loads, multiplies, and finishes the dot product with xor-shuffles inside the
-// group.  The G results of a batch are written with one coalesced store.
-// Rows longer than LONG_ROW entries go through the chunk work list (scratch
-// memory) and a second launch where a whole CTA shares one chunk.
+// One warp owns a row i (rows are dealt to warps round-robin, so the long rows
+// that sit together in a power-law matrix spread over all SMs).  The warp keeps
+// X[i,:] in registers, split over groups of G lanes (2*NI doubles per lane); it
+// loads 32 column coordinates with one coalesced streaming load and then works
+// on 32/G stored entries at a time: each group gathers its Y[j,:] with 128-bit
+// loads, multiplies, and finishes its dot product with xor-shuffles.  All
+// groups of a warp work on the same row, so lanes never diverge on row length.
+// The 32 results of a batch are scaled by S.val and written with one coalesced
+// store.  Rows longer than LONG_ROW entries are cut into chunks that go to a
+// work list in scratch memory; a second launch hands each chunk to a warp.
 //
 // Bound: HBM.  Algorithmic bytes = 8(n+1) + 24 nnz + 8 K (nrows + ncols).
 #include "common.cuh"
@@ -14,42 +17,52 @@
 namespace cb200 {
 
 static const int SDDMM_THREADS = 256;
-static const int SDDMM_PASSES = 2;
-static const int64_t SDDMM_LONG_ROW = 512;
+static const int64_t SDDMM_LONG_ROW = 1024;
 static const int64_t SDDMM_CHUNK = 512;
 
+// Entries [s, e) of row `row`; xr holds this lane's part of X[row,:].
 template <int G, int NI>
 __device__ __forceinline__ void sample_range(const double2 (&xr)[NI], const int64_t *__restrict__ crd,
                                              const double *__restrict__ sval,
                                              const double *__restrict__ y, int64_t ldy,
-                                             double *__restrict__ out, int64_t s, int64_t e, int l,
-                                             unsigned gmask, int k2)
+                                             double *__restrict__ out, int64_t s, int64_t e, int lane,
+                                             int k2)
 {
-    for (int64_t base = s; base < e; base += G) {
-        int64_t p = base + l;
+    constexpr int P = 32 / G;                 // entries in flight per step
+    const int g = lane / G, l = lane % G;
+    for (int64_t base = s; base < e; base += 32) {
+        const int64_t p = base + lane;
         int64_t c = 0;
         if (p < e) c = ld_stream(crd + p);
-        int n = (e - base) < G ? (int)(e - base) : G;
+        const int n = (e - base) < 32 ? (int)(e - base) : 32;
         double mine = 0.0;
+        const int steps = (n + P - 1) / P;
 #pragma unroll 2
-        for (int t = 0; t < n; t++) {
-            int64_t cc = __shfl_sync(gmask, (long long)c, t, G);
-            const double2 *yr = (const double2 *)(y + cc * ldy);
+        for (int t = 0; t < steps; t++) {
+            const int idx = t * P + g;        // entry of this batch handled by my group
+            const int64_t cc = __shfl_sync(0xffffffffu, (long long)c, idx & 31);
             double d0 = 0.0, d1 = 0.0;
+            if (idx < n) {
+                const double2 *yr = (const double2 *)(y + cc * ldy);
 #pragma unroll
-            for (int i = 0; i < NI; i++) {
-                if (l + i * G < k2) {
-                    double2 yy = __ldg(yr + l + i * G);
-                    d0 = fma(xr[i].x, yy.x, d0);
-                    d1 = fma(xr[i].y, yy.y, d1);
+                for (int i = 0; i < NI; i++) {
+                    if (l + i * G < k2) {
+                        double2 yy = __ldg(yr + l + i * G);
+                        d0 = fma(xr[i].x, yy.x, d0);
+                        d1 = fma(xr[i].y, yy.y, d1);
+                    }
                 }
             }
             double d = d0 + d1;
 #pragma unroll
-            for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(gmask, d, o, G);
+            for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            // a batch has at most 32 / P = G steps, so lane l == t of each group can keep step t's result
             if (l == t) mine = d;
         }
-        if (p < e) out[p] = ld_stream(sval + p) * mine;
+        // lane (g, l) now holds the result of batch entry l*P + g: a permutation of the batch,
+        // so the store below is one coalesced 256-byte write per warp
+        const int idx = l * P + g;
+        if (idx < n) out[base + idx] = ld_stream(sval + base + idx) * mine;
     }
 }
 
@@ -60,7 +73,7 @@ __device__ __forceinline__ void load_x(double2 (&xr)[NI], const double *__restri
     const double2 *xp = (const double2 *)(x + row * ldx);
 #pragma unroll
     for (int i = 0; i < NI; i++)
-        xr[i] = (l + i * G < k2) ? xp[l + i * G] : make_double2(0.0, 0.0);
+        xr[i] = (l + i * G < k2) ? __ldg(xp + l + i * G) : make_double2(0.0, 0.0);
 }
 
 template <int G, int NI>
@@ -70,20 +83,15 @@ sddmm_rows_kernel(int64_t nrows, const int64_t *__restrict__ pos, const int64_t 
                   const double *__restrict__ y, int64_t ldy, double *__restrict__ out, int k,
                   WorkHeader *hdr, Chunk *chunks, unsigned chunk_cap)
 {
-    constexpr int GROUPS = SDDMM_THREADS / G;
-    constexpr int ROWS = GROUPS * SDDMM_PASSES;
-    const int g = threadIdx.x / G, l = threadIdx.x % G;
     const int lane = threadIdx.x & 31;
-    const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << (lane & ~(G - 1)));
     const int k2 = k / 2;
-    const int64_t row0 = (int64_t)blockIdx.x * ROWS;
-    for (int pass = 0; pass < SDDMM_PASSES; pass++) {
-        int64_t r = row0 + pass * GROUPS + g;
-        if (r >= nrows) break;
-        int64_t s = pos[r], e = pos[r + 1];
+    const int64_t warp = ((int64_t)blockIdx.x * SDDMM_THREADS + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * SDDMM_THREADS) >> 5;
+    for (int64_t r = warp; r < nrows; r += nwarps) {
+        const int64_t s = pos[r], e = pos[r + 1];
         if (s == e) continue;
         if (e - s > SDDMM_LONG_ROW) {
-            if (l == 0) {
+            if (lane == 0) {
                 unsigned n = (unsigned)((e - s + SDDMM_CHUNK - 1) / SDDMM_CHUNK);
                 unsigned at = atomicAdd(&hdr->count, n);
                 if (at + n <= chunk_cap) {
@@ -98,8 +106,8 @@ sddmm_rows_kernel(int64_t nrows, const int64_t *__restrict__ pos, const int64_t 
             continue;
         }
         double2 xr[NI];
-        load_x<G, NI>(xr, x, ldx, r, l, k2);
-        sample_range<G, NI>(xr, crd, sval, y, ldy, out, s, e, l, gmask, k2);
+        load_x<G, NI>(xr, x, ldx, r, lane % G, k2);
+        sample_range<G, NI>(xr, crd, sval, y, ldy, out, s, e, lane, k2);
     }
 }
 
@@ -110,31 +118,23 @@ sddmm_chunks_kernel(const int64_t *__restrict__ pos, const int64_t *__restrict__
                     const double *__restrict__ y, int64_t ldy, double *__restrict__ out, int k,
                     const WorkHeader *hdr, const Chunk *chunks, unsigned chunk_cap)
 {
-    constexpr int GROUPS = SDDMM_THREADS / G;
-    const int g = threadIdx.x / G, l = threadIdx.x % G;
     const int lane = threadIdx.x & 31;
-    const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << (lane & ~(G - 1)));
     const int k2 = k / 2;
+    const unsigned warp = (blockIdx.x * SDDMM_THREADS + threadIdx.x) >> 5;
+    const unsigned nwarps = (gridDim.x * SDDMM_THREADS) >> 5;
     unsigned count = hdr->count;
     if (count > chunk_cap) count = 0;
-    for (unsigned w = blockIdx.x; w < count; w += gridDim.x) {
+    for (unsigned w = warp; w < count; w += nwarps) {
         const Chunk ch = chunks[w];
         int64_t cend = pos[ch.row + 1];
         if (cend > ch.begin + SDDMM_CHUNK) cend = ch.begin + SDDMM_CHUNK;
-        // contiguous sub-ranges whose length is a multiple of G keep the stores coalesced
-        int64_t per = (cend - ch.begin + GROUPS - 1) / GROUPS;
-        per = (per + G - 1) / G * G;
-        int64_t s = ch.begin + (int64_t)g * per, e = s + per;
-        if (e > cend) e = cend;
-        if (s < e) {
-            double2 xr[NI];
-            load_x<G, NI>(xr, x, ldx, ch.row, l, k2);
-            sample_range<G, NI>(xr, crd, sval, y, ldy, out, s, e, l, gmask, k2);
-        }
+        double2 xr[NI];
+        load_x<G, NI>(xr, x, ldx, ch.row, lane % G, k2);
+        sample_range<G, NI>(xr, crd, sval, y, ldy, out, ch.begin, cend, lane, k2);
     }
 }
 
-// Any K and alignment: one thread per stored entry (correctness path).
+// Any K and alignment: one thread per row (correctness path).
 __global__ void __launch_bounds__(256)
 sddmm_scalar_kernel(int64_t nrows, const int64_t *__restrict__ pos, const int64_t *__restrict__ crd,
                     const double *__restrict__ sval, const double *__restrict__ x, int64_t ldx,
@@ -157,10 +157,11 @@ static int launch_sddmm(int64_t nrows, int64_t nnz, const int64_t *pos, const in
                         int64_t ldy, double *out, int k, WorkHeader *hdr, Chunk *chunks,
                         unsigned cap, cudaStream_t st)
 {
-    constexpr int ROWS = (SDDMM_THREADS / G) * SDDMM_PASSES;
-    unsigned grid = (unsigned)ceil_div(nrows, ROWS);
-    sddmm_rows_kernel<G, NI><<<grid, SDDMM_THREADS, 0, st>>>(nrows, pos, crd, sval, x, ldx, y, ldy, out,
-                                                           k, hdr, chunks, cap);
+    int64_t grid = ceil_div(nrows, SDDMM_THREADS / 32);
+    const int64_t full = (int64_t)sm_count() * 16;
+    if (grid > full) grid = full;
+    sddmm_rows_kernel<G, NI><<<(unsigned)grid, SDDMM_THREADS, 0, st>>>(nrows, pos, crd, sval, x, ldx, y, ldy,
+                                                                     out, k, hdr, chunks, cap);
     CB_LAUNCH_CHECK();
     if (nnz > SDDMM_LONG_ROW) {
         sddmm_chunks_kernel<G, NI><<<(unsigned)sm_count() * 8, SDDMM_THREADS, 0, st>>>(

@@ -115,11 +115,11 @@ spmm_rows_kernel(int64_t nrows, const int64_t *__restrict__ row_ids,
             if (l + i * T < ncol2) {
                 double2 o = acc[i];
                 if (accumulate) {
-                    double2 old = crow[l + i * T];
+                    double2 old = __ldcs(crow + l + i * T);
                     o.x += old.x;
                     o.y += old.y;
                 }
-                crow[l + i * T] = o;
+                __stcs(crow + l + i * T, o);   // written once, never re-read: keep it out of B's way in L2
             }
         }
     }

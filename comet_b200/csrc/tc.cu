@@ -1,14 +1,23 @@
 // Masked SpGEMM reduced to a scalar under plus-pair:
-//   count = sum over stored A[i,k] of | row k of B  intersect  row i of M |
+//   count = sum over stored A[i,k] of the number of entries of row k of B whose
+//           column is stored in row i of M
 // which is SUM(C<M,push> = A*B) with every product worth 1.  With A = B = M = L
 // (strict lower triangle of a symmetric graph) it is the triangle count.
 //
-// Work is split by stored entries of A, not by rows: a group of 8 lanes takes
-// 32 consecutive entries, finds their row once by binary search in A.pos, and
-// for each entry walks the shorter of the two sorted lists with its lanes while
-// binary-searching the longer one.  (The reference probes a bitmap of the mask
-// row with every element of B's row; the number of hits is the same, the
-// number of probes is min(len) * log(max len) instead of len(B row).)
+// Same structure as the reference's push mask (set the bits of M's row i, test
+// every product's column, clear them).  The bit array over all columns does not
+// fit shared memory, so the mask row is held there as a one-hash Bloom filter
+// (one bit test, no loop, rejects almost every miss) backed by an open-addressing
+// hash set that confirms the few positives.  Rows are binned by the length of
+// their mask row:
+//   <= 128 entries   one warp per row
+//   <= 2048 entries  one CTA per row
+//   longer           cut into units of (8192 mask entries) x (2048 entries of A),
+//                    one CTA per unit, so a huge row spreads over many SMs
+// and rows / units are handed out dynamically (one atomic each), because the work
+// per row (sum of the lengths of the B rows it touches) is very uneven.
+// Every element of every touched B row is read (coalesced, int32) and tested
+// once per mask segment, so the number of probes equals the reference's.
 // Coordinates are narrowed to int32 once per call (scratch memory).
 //
 // Counts are exact int64; no floating point is involved.
@@ -16,73 +25,270 @@
 
 namespace cb200 {
 
-static const int TC_THREADS = 256;
-static const int TC_GROUP = 8;
-static const int TC_EDGES = 32;   // entries of A per group per step
+static const int TC_WARP_MAX = 128;      // mask-row length handled by a warp
+static const int TC_WARP_TAB = 8;        // log2 slots of its hash set
+static const int TC_WARP_BLOOM = 12;     // log2 bits of its Bloom filter
+static const int TC_WARPS = 8;           // warps per CTA in the warp kernel
+static const int TC_MID_MAX = 2048;
+static const int TC_MID_TAB = 12;
+static const int TC_MID_BLOOM = 15;
+static const int TC_BIG_SEG = 8192;      // mask entries per unit
+static const int TC_BIG_SLICE = 2048;    // entries of A per unit
+static const int TC_BIG_TAB = 14;
+static const int TC_BIG_BLOOM = 17;
 
-__device__ __forceinline__ bool contains(const int32_t *__restrict__ a, int64_t lo, int64_t hi,
-                                         int32_t key)
+struct TcUnit {
+    int32_t row;
+    int32_t mask_off;    // first mask entry of the unit, relative to the row
+    int32_t edge_off;    // first entry of A of the unit, relative to the row
+};
+
+struct TcHeader {
+    unsigned count[4];   // rows in the warp bin, rows in the CTA bin, units, rows whose units did not fit
+    unsigned next[4];    // next item to hand out per list
+};
+
+template <int LOG2>
+__device__ __forceinline__ unsigned tc_slot(int32_t j)
 {
-    while (lo < hi) {
-        int64_t mid = (lo + hi) >> 1;
-        int32_t v = __ldg(a + mid);
-        if (v == key) return true;
-        if (v < key) lo = mid + 1; else hi = mid;
-    }
-    return false;
+    return ((uint32_t)j * 0x9E3779B1u) >> (32 - LOG2);
 }
 
-__global__ void __launch_bounds__(TC_THREADS)
-masked_pair_count_kernel(int64_t row_lo, int64_t row_hi, const int64_t *__restrict__ apos,
-                         const int32_t *__restrict__ acrd, const int64_t *__restrict__ bpos,
-                         const int32_t *__restrict__ bcrd, const int64_t *__restrict__ mpos,
-                         const int32_t *__restrict__ mcrd, unsigned long long *__restrict__ count)
+template <int LOG2>
+__device__ __forceinline__ void tc_insert(int32_t *tab, int32_t j)
 {
-    __shared__ unsigned long long s_part[TC_THREADS / 32];
-    const int l = threadIdx.x % TC_GROUP;
-    const int64_t group = ((int64_t)blockIdx.x * TC_THREADS + threadIdx.x) / TC_GROUP;
-    const int64_t ngroups = (int64_t)gridDim.x * TC_THREADS / TC_GROUP;
-    const int64_t e_begin = apos[row_lo], e_end = apos[row_hi];
-    const int64_t nchunks = (e_end - e_begin + TC_EDGES - 1) / TC_EDGES;
-    unsigned long long hits = 0;
-    for (int64_t ch = group; ch < nchunks; ch += ngroups) {
-        int64_t p0 = e_begin + ch * TC_EDGES;
-        int64_t p1 = p0 + TC_EDGES < e_end ? p0 + TC_EDGES : e_end;
-        // row of p0: last r in [row_lo, row_hi) with apos[r] <= p0
-        int64_t lo = row_lo, hi = row_hi;
-        while (hi - lo > 1) {
-            int64_t mid = (lo + hi) >> 1;
-            if (apos[mid] <= p0) lo = mid; else hi = mid;
+    unsigned h = tc_slot<LOG2>(j);
+    for (int probe = 0; probe < (1 << LOG2); probe++) {
+        int32_t old = atomicCAS(&tab[h], -1, j);
+        if (old == -1 || old == j) return;
+        h = (h + 1) & ((1u << LOG2) - 1u);
+    }
+}
+
+template <int LOG2>
+__device__ __forceinline__ unsigned tc_confirm(const int32_t *tab, int32_t j)
+{
+    unsigned h = tc_slot<LOG2>(j);
+    for (int probe = 0; probe < (1 << LOG2); probe++) {
+        int32_t k = tab[h];
+        if (k == j) return 1u;
+        if (k == -1) return 0u;
+        h = (h + 1) & ((1u << LOG2) - 1u);
+    }
+    return 0u;
+}
+
+// Bloom filter with a single hash: bit = top BLOOM bits of the multiplicative hash.
+template <int BLOOM>
+__device__ __forceinline__ unsigned tc_bit(int32_t j)
+{
+    return ((uint32_t)j * 0x85EBCA6Bu) >> (32 - BLOOM);
+}
+
+template <int LOG2, int BLOOM>
+__device__ __forceinline__ unsigned tc_probe(const int32_t *tab, const uint32_t *bloom, int32_t j)
+{
+    const unsigned b = tc_bit<BLOOM>(j);
+    if (!((bloom[b >> 5] >> (b & 31)) & 1u)) return 0u;
+    return tc_confirm<LOG2>(tab, j);
+}
+
+// Clears and fills filter and set with mask entries [ms, me); `nthreads` threads with index `tid` cooperate.
+template <int LOG2, int BLOOM>
+__device__ __forceinline__ void tc_fill(int32_t *tab, uint32_t *bloom, const int32_t *__restrict__ mcrd,
+                                        int64_t ms, int64_t me, int tid, int nthreads, bool block)
+{
+    for (int s = tid; s < (1 << LOG2); s += nthreads) tab[s] = -1;
+    for (int s = tid; s < (1 << (BLOOM - 5)); s += nthreads) bloom[s] = 0u;
+    if (block) __syncthreads(); else __syncwarp();
+    for (int64_t t = ms + tid; t < me; t += nthreads) {
+        const int32_t j = mcrd[t];
+        tc_insert<LOG2>(tab, j);
+        const unsigned b = tc_bit<BLOOM>(j);
+        atomicOr(&bloom[b >> 5], 1u << (b & 31));
+    }
+    if (block) __syncthreads(); else __syncwarp();
+}
+
+// Streams the B rows named by entries [as, ae) of A's row and counts the elements
+// found in the table.  The `nparts` warps that share the row take batches of 32
+// consecutive entries round-robin (`part` = this warp's index).  A batch's B-row
+// bounds are fetched by the 32 lanes at once and broadcast with shuffles, so the
+// dependent chain acrd -> bpos -> bcrd is paid once per 32 entries; elements are
+// loaded four at a time per lane before they are probed.
+template <int LOG2, int BLOOM>
+__device__ __forceinline__ unsigned long long tc_stream_rows(const int32_t *tab, const uint32_t *bloom,
+                                                            int64_t as, int64_t ae,
+                                                            int part, int nparts, int lane,
+                                                            const int32_t *__restrict__ acrd,
+                                                            const int64_t *__restrict__ bpos,
+                                                            const int32_t *__restrict__ bcrd)
+{
+    unsigned long long total = 0;
+    for (int64_t pb = as + 32 * (int64_t)part; pb < ae; pb += 32 * (int64_t)nparts) {
+        int64_t bs_l = 0, be_l = 0;
+        if (pb + lane < ae) {
+            const int64_t k = __ldg(acrd + pb + lane);
+            bs_l = __ldg(bpos + k);
+            be_l = __ldg(bpos + k + 1);
         }
-        int64_t i = lo, i_end = apos[i + 1];
-        int64_t ms = mpos[i], me = mpos[i + 1];
-        for (int64_t p = p0; p < p1; p++) {
-            while (p >= i_end) {   // skip to the row that holds p (empty rows in between)
-                i++;
-                i_end = apos[i + 1];
-                ms = mpos[i];
-                me = mpos[i + 1];
+        const int n = (ae - pb) < 32 ? (int)(ae - pb) : 32;
+        unsigned h32 = 0;
+        for (int t = 0; t < n; t++) {
+            const int64_t bs = __shfl_sync(0xffffffffu, (long long)bs_l, t);
+            const int64_t be = __shfl_sync(0xffffffffu, (long long)be_l, t);
+            for (int64_t q = bs + lane; q < be; q += 128) {
+                int32_t j[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) j[u] = (q + 32 * u < be) ? __ldg(bcrd + q + 32 * u) : 0;
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (q + 32 * u < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, j[u]);
             }
-            if (ms == me) continue;
-            const int64_t k = acrd[p];
-            const int64_t bs = bpos[k], be = bpos[k + 1];
-            if (bs == be) continue;
-            if (be - bs <= me - ms) {
-                for (int64_t q = bs + l; q < be; q += TC_GROUP)
-                    hits += contains(mcrd, ms, me, __ldg(bcrd + q)) ? 1 : 0;
-            } else {
-                for (int64_t q = ms + l; q < me; q += TC_GROUP)
-                    hits += contains(bcrd, bs, be, __ldg(mcrd + q)) ? 1 : 0;
+        }
+        total += h32;
+    }
+    return total;
+}
+
+__global__ void __launch_bounds__(256)
+tc_bin_kernel(int64_t row_lo, int64_t row_hi, const int64_t *__restrict__ apos,
+              const int64_t *__restrict__ mpos, TcHeader *hdr, int32_t *__restrict__ list0,
+              int32_t *__restrict__ list1, int32_t *__restrict__ slow, TcUnit *__restrict__ units,
+              unsigned unit_cap)
+{
+    int64_t r = row_lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int bin = -1;
+    int64_t al = 0, ml = 0;
+    if (r < row_hi) {
+        al = apos[r + 1] - apos[r];
+        ml = mpos[r + 1] - mpos[r];
+        if (al > 0 && ml > 0) bin = ml <= TC_WARP_MAX ? 0 : (ml <= TC_MID_MAX ? 1 : 2);
+    }
+    // one atomic per warp and bin
+    const int lane = threadIdx.x & 31;
+    for (int b = 0; b < 2; b++) {
+        unsigned m = __ballot_sync(0xffffffffu, bin == b);
+        if (!m) continue;
+        unsigned base = 0;
+        int leader = __ffs(m) - 1;
+        if (lane == leader) base = atomicAdd(&hdr->count[b], (unsigned)__popc(m));
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (bin == b) (b == 0 ? list0 : list1)[base + __popc(m & ((1u << lane) - 1u))] = (int32_t)r;
+    }
+    if (bin == 2) {
+        const unsigned nseg = (unsigned)((ml + TC_BIG_SEG - 1) / TC_BIG_SEG);
+        const unsigned nsl = (unsigned)((al + TC_BIG_SLICE - 1) / TC_BIG_SLICE);
+        const unsigned long long want = (unsigned long long)nseg * nsl;
+        bool placed = false;
+        if (want <= unit_cap) {
+            unsigned at = atomicAdd(&hdr->count[2], (unsigned)want);
+            if ((unsigned long long)at + want <= unit_cap) {
+                for (unsigned a = 0; a < nseg; a++)
+                    for (unsigned b = 0; b < nsl; b++) {
+                        TcUnit u;
+                        u.row = (int32_t)r;
+                        u.mask_off = (int32_t)(a * TC_BIG_SEG);
+                        u.edge_off = (int32_t)(b * TC_BIG_SLICE);
+                        units[at + a * nsl + b] = u;
+                    }
+                placed = true;
+            } else if (at < unit_cap) {
+                // the reservation ran past the end: neutralise the part of it that lies inside the list
+                for (unsigned t = at; t < unit_cap; t++) { TcUnit u; u.row = -1; u.mask_off = 0; u.edge_off = 0; units[t] = u; }
             }
+        }
+        if (!placed) slow[atomicAdd(&hdr->count[3], 1u)] = (int32_t)r;   // whole row by one CTA
+    }
+}
+
+__global__ void __launch_bounds__(TC_WARPS * 32)
+tc_warp_kernel(TcHeader *hdr, const int32_t *__restrict__ list, const int64_t *__restrict__ apos,
+               const int32_t *__restrict__ acrd, const int64_t *__restrict__ bpos,
+               const int32_t *__restrict__ bcrd, const int64_t *__restrict__ mpos,
+               const int32_t *__restrict__ mcrd, unsigned long long *__restrict__ count)
+{
+    __shared__ int32_t s_tab[TC_WARPS][1 << TC_WARP_TAB];
+    __shared__ uint32_t s_bloom[TC_WARPS][1 << (TC_WARP_BLOOM - 5)];
+    __shared__ unsigned long long s_part[TC_WARPS];
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned nlist = hdr->count[0];
+    unsigned long long hits = 0;
+    while (true) {
+        unsigned idx = 0;
+        if (lane == 0) idx = atomicAdd(&hdr->next[0], 1u);
+        idx = __shfl_sync(0xffffffffu, idx, 0);
+        if (idx >= nlist) break;
+        const int64_t i = list[idx];
+        tc_fill<TC_WARP_TAB, TC_WARP_BLOOM>(s_tab[w], s_bloom[w], mcrd, mpos[i], mpos[i + 1], lane, 32, false);
+        hits += tc_stream_rows<TC_WARP_TAB, TC_WARP_BLOOM>(s_tab[w], s_bloom[w], apos[i], apos[i + 1], 0, 1,
+                                                           lane, acrd, bpos, bcrd);
+        __syncwarp();
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) hits += __shfl_xor_sync(0xffffffffu, hits, o);
+    if (lane == 0) s_part[w] = hits;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+        for (int i = 0; i < TC_WARPS; i++) t += s_part[i];
+        if (t) atomicAdd(count, t);
+    }
+}
+
+// MODE 0: list of rows, whole row per CTA (mask taken in segments of SEG entries).
+// MODE 1: list of units (mask segment x slice of A's entries).
+template <int THREADS, int LOG2, int BLOOM, int SEG, int MODE>
+__global__ void __launch_bounds__(THREADS)
+tc_block_kernel(TcHeader *hdr, int which, const int32_t *__restrict__ list,
+                const TcUnit *__restrict__ units, const int64_t *__restrict__ apos,
+                const int32_t *__restrict__ acrd, const int64_t *__restrict__ bpos,
+                const int32_t *__restrict__ bcrd, const int64_t *__restrict__ mpos,
+                const int32_t *__restrict__ mcrd, unsigned unit_cap,
+                unsigned long long *__restrict__ count)
+{
+    extern __shared__ int32_t s_dyn_tc[];
+    __shared__ unsigned long long s_part[THREADS / 32];
+    __shared__ unsigned s_idx;
+    int32_t *tab = s_dyn_tc;
+    uint32_t *bloom = (uint32_t *)(s_dyn_tc + (1 << LOG2));
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned nlist = hdr->count[which];
+    if (MODE == 1 && nlist > unit_cap) nlist = unit_cap;
+    unsigned long long hits = 0;
+    while (true) {
+        if (threadIdx.x == 0) s_idx = atomicAdd(&hdr->next[which], 1u);
+        __syncthreads();
+        const unsigned idx = s_idx;
+        __syncthreads();
+        if (idx >= nlist) break;
+        int64_t i, ms, me, as, ae;
+        if (MODE == 1) {
+            const TcUnit u = units[idx];
+            if (u.row < 0) continue;
+            i = u.row;
+            ms = mpos[i] + u.mask_off;
+            me = mpos[i + 1] < ms + SEG ? mpos[i + 1] : ms + SEG;
+            as = apos[i] + u.edge_off;
+            ae = apos[i + 1] < as + TC_BIG_SLICE ? apos[i + 1] : as + TC_BIG_SLICE;
+        } else {
+            i = list[idx];
+            ms = mpos[i]; me = mpos[i + 1]; as = apos[i]; ae = apos[i + 1];
+        }
+        for (int64_t seg = ms; seg < me; seg += SEG) {
+            const int64_t seg_end = seg + SEG < me ? seg + SEG : me;
+            tc_fill<LOG2, BLOOM>(tab, bloom, mcrd, seg, seg_end, threadIdx.x, THREADS, true);
+            hits += tc_stream_rows<LOG2, BLOOM>(tab, bloom, as, ae, w, THREADS / 32, lane, acrd, bpos, bcrd);
+            __syncthreads();
         }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) hits += __shfl_xor_sync(0xffffffffu, hits, o);
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = hits;
+    if (lane == 0) s_part[w] = hits;
     __syncthreads();
     if (threadIdx.x == 0) {
         unsigned long long t = 0;
-        for (int w = 0; w < TC_THREADS / 32; w++) t += s_part[w];
+        for (int i = 0; i < THREADS / 32; i++) t += s_part[i];
         if (t) atomicAdd(count, t);
     }
 }
@@ -94,7 +300,8 @@ int masked_pair_count(int64_t row_lo, int64_t row_hi, int64_t ncols, int64_t nnz
 {
     CB_CUDA(cudaMemsetAsync(count_dev, 0, sizeof(int64_t), st));
     if (row_hi <= row_lo || nnz_a <= 0 || nnz_b <= 0 || nnz_m <= 0) return 0;
-    if (ncols >= 0x7fffffffLL) return fail("masked count: more than 2^31-1 columns is not supported");
+    if (ncols >= 0x7fffffffLL || row_hi >= 0x7fffffffLL)
+        return fail("masked count: more than 2^31-1 rows or columns is not supported");
     if ((((uintptr_t)acrd | (uintptr_t)bcrd | (uintptr_t)mcrd) & 15) != 0)
         return fail("masked count: crd arrays must be 16-byte aligned");
     void *a32 = nullptr, *b32 = nullptr, *m32 = nullptr;
@@ -111,14 +318,41 @@ int masked_pair_count(int64_t row_lo, int64_t row_hi, int64_t ncols, int64_t nnz
         CB_TRY(scratch(SLOT_NARROW_M, (size_t)nnz_m * sizeof(int32_t), &m32));
         CB_TRY(narrow_i64_to_i32(mcrd, (int32_t *)m32, nnz_m, st));
     }
-    int64_t groups = ceil_div(nnz_a, TC_EDGES);
-    int64_t blocks = ceil_div(groups * TC_GROUP, TC_THREADS);
-    int64_t cap = (int64_t)sm_count() * 64;
-    if (blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
-    masked_pair_count_kernel<<<(unsigned)blocks, TC_THREADS, 0, st>>>(
-        row_lo, row_hi, apos, (const int32_t *)a32, bpos, (const int32_t *)b32, mpos,
-        (const int32_t *)m32, (unsigned long long *)count_dev);
+    const int64_t nrows = row_hi - row_lo;
+    const size_t unit_cap = (size_t)(nnz_a / 256 + 65536);
+    void *lists = nullptr, *hdrp = nullptr;
+    CB_TRY(scratch(SLOT_BINS, (size_t)nrows * 3 * sizeof(int32_t) + unit_cap * sizeof(TcUnit), &lists));
+    CB_TRY(scratch(SLOT_MISC, sizeof(TcHeader), &hdrp));
+    TcHeader *hdr = (TcHeader *)hdrp;
+    int32_t *list0 = (int32_t *)lists, *list1 = list0 + nrows, *slow = list1 + nrows;
+    TcUnit *units = (TcUnit *)(slow + nrows);
+    CB_CUDA(cudaMemsetAsync(hdr, 0, sizeof(TcHeader), st));
+    tc_bin_kernel<<<(unsigned)ceil_div(nrows, 256), 256, 0, st>>>(row_lo, row_hi, apos, mpos, hdr, list0,
+                                                                   list1, slow, units, (unsigned)unit_cap);
+    CB_LAUNCH_CHECK();
+    const int32_t *A = (const int32_t *)a32, *B = (const int32_t *)b32, *M = (const int32_t *)m32;
+    unsigned long long *cnt = (unsigned long long *)count_dev;
+    const unsigned sms = (unsigned)sm_count();
+    {   // longest rows first
+        constexpr int T = 512;
+        const size_t smem = (sizeof(int32_t) << TC_BIG_TAB) + (sizeof(uint32_t) << (TC_BIG_BLOOM - 5));
+        auto kunits = tc_block_kernel<T, TC_BIG_TAB, TC_BIG_BLOOM, TC_BIG_SEG, 1>;
+        auto kslow = tc_block_kernel<T, TC_BIG_TAB, TC_BIG_BLOOM, TC_BIG_SEG, 0>;
+        CB_CUDA(cudaFuncSetAttribute(kunits, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        CB_CUDA(cudaFuncSetAttribute(kslow, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kunits<<<sms * 2, T, smem, st>>>(hdr, 2, nullptr, units, apos, A, bpos, B, mpos, M, (unsigned)unit_cap, cnt);
+        CB_LAUNCH_CHECK();
+        kslow<<<sms, T, smem, st>>>(hdr, 3, slow, nullptr, apos, A, bpos, B, mpos, M, (unsigned)unit_cap, cnt);
+        CB_LAUNCH_CHECK();
+    }
+    {
+        constexpr int T = 256;
+        const size_t smem = (sizeof(int32_t) << TC_MID_TAB) + (sizeof(uint32_t) << (TC_MID_BLOOM - 5));
+        tc_block_kernel<T, TC_MID_TAB, TC_MID_BLOOM, TC_MID_MAX, 0><<<sms * 8, T, smem, st>>>(
+            hdr, 1, list1, nullptr, apos, A, bpos, B, mpos, M, (unsigned)unit_cap, cnt);
+        CB_LAUNCH_CHECK();
+    }
+    tc_warp_kernel<<<sms * 8, TC_WARPS * 32, 0, st>>>(hdr, list0, apos, A, bpos, B, mpos, M, cnt);
     CB_LAUNCH_CHECK();
     return 0;
 }

@@ -274,8 +274,9 @@ COMET_B200_EXPORT int32_t comet_b200_dev_spgemm_numeric_f64_i64(int64_t handle, 
                                                                 void *stream);
 
 /* *count_dev (device memory, int64) receives the number of products A[i,k]*B[k,j]
-   with (i,j) stored in M, over rows [row_lo, row_hi) of A and M.  Rows of B and M
-   must hold strictly ascending column coordinates (no duplicates). */
+   with (i,j) stored in M, over rows [row_lo, row_hi) of A and M.  A duplicate
+   coordinate in M counts once (a mask bit), one in A or B counts per occurrence,
+   as in the reference's loops; no ordering of coordinates is required. */
 COMET_B200_EXPORT int32_t comet_b200_dev_masked_spgemm_count_f64_i64(
     int64_t row_lo, int64_t row_hi, int64_t ncols, int64_t nnz_a, int64_t nnz_b, int64_t nnz_m,
     const int64_t *apos, const int64_t *acrd, const int64_t *bpos, const int64_t *bcrd,
