@@ -111,21 +111,33 @@ __device__ __forceinline__ void tc_fill(int32_t *tab, uint32_t *bloom, const int
 }
 
 // Streams the B rows named by entries [as, ae) of A's row and counts the elements
-// found in the table.  The `nparts` warps that share the row take batches of 32
-// consecutive entries round-robin (`part` = this warp's index).  A batch's B-row
-// bounds are fetched by the 32 lanes at once and broadcast with shuffles, so the
-// dependent chain acrd -> bpos -> bcrd is paid once per 32 entries; elements are
-// loaded four at a time per lane before they are probed.
+// found in the filter + set.  Entries are taken in batches of 32: with `next`
+// null the calling warp walks all batches itself; otherwise the warps of a CTA
+// draw batch numbers from the shared counter `*next`, so a warp that meets short
+// B rows simply draws more batches.  A batch's B-row bounds are fetched by the 32
+// lanes at once and broadcast with shuffles, so the dependent chain
+// acrd -> bpos -> bcrd is paid once per 32 entries.  Elements are read with
+// 128-bit loads (four coordinates per lane, two loads in flight); a B row is
+// entered at the 16-byte boundary below its first element and the elements
+// outside [bs, be) are masked off.
 template <int LOG2, int BLOOM>
 __device__ __forceinline__ unsigned long long tc_stream_rows(const int32_t *tab, const uint32_t *bloom,
-                                                            int64_t as, int64_t ae,
-                                                            int part, int nparts, int lane,
-                                                            const int32_t *__restrict__ acrd,
+                                                            int64_t as, int64_t ae, unsigned *next,
+                                                            int lane, const int32_t *__restrict__ acrd,
                                                             const int64_t *__restrict__ bpos,
                                                             const int32_t *__restrict__ bcrd)
 {
     unsigned long long total = 0;
-    for (int64_t pb = as + 32 * (int64_t)part; pb < ae; pb += 32 * (int64_t)nparts) {
+    const int64_t nbatches = (ae - as + 31) >> 5;
+    int64_t batch = 0;
+    while (true) {
+        if (next) {
+            unsigned b = 0;
+            if (lane == 0) b = atomicAdd(next, 1u);
+            batch = __shfl_sync(0xffffffffu, b, 0);
+        }
+        if (batch >= nbatches) break;
+        const int64_t pb = as + (batch << 5);
         int64_t bs_l = 0, be_l = 0;
         if (pb + lane < ae) {
             const int64_t k = __ldg(acrd + pb + lane);
@@ -137,16 +149,35 @@ __device__ __forceinline__ unsigned long long tc_stream_rows(const int32_t *tab,
         for (int t = 0; t < n; t++) {
             const int64_t bs = __shfl_sync(0xffffffffu, (long long)bs_l, t);
             const int64_t be = __shfl_sync(0xffffffffu, (long long)be_l, t);
-            for (int64_t q = bs + lane; q < be; q += 128) {
-                int32_t j[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) j[u] = (q + 32 * u < be) ? __ldg(bcrd + q + 32 * u) : 0;
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if (q + 32 * u < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, j[u]);
+            for (int64_t q = (bs & ~(int64_t)3) + 4 * lane; q < be; q += 256) {
+                int4 v0 = make_int4(0, 0, 0, 0), v1 = make_int4(0, 0, 0, 0);
+                v0 = __ldg((const int4 *)(bcrd + q));
+                const bool two = q + 128 < be;
+                if (two) v1 = __ldg((const int4 *)(bcrd + q + 128));
+                if (q >= bs && q + 3 < be) {
+                    h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.x) + tc_probe<LOG2, BLOOM>(tab, bloom, v0.y) +
+                           tc_probe<LOG2, BLOOM>(tab, bloom, v0.z) + tc_probe<LOG2, BLOOM>(tab, bloom, v0.w);
+                } else {
+                    if (q >= bs) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.x);
+                    if (q + 1 >= bs && q + 1 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.y);
+                    if (q + 2 >= bs && q + 2 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.z);
+                    if (q + 3 >= bs && q + 3 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.w);
+                }
+                if (two) {
+                    const int64_t r = q + 128;           // r >= bs always: it lies past the first vector
+                    if (r + 3 < be) {
+                        h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.x) + tc_probe<LOG2, BLOOM>(tab, bloom, v1.y) +
+                               tc_probe<LOG2, BLOOM>(tab, bloom, v1.z) + tc_probe<LOG2, BLOOM>(tab, bloom, v1.w);
+                    } else {
+                        h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.x);
+                        if (r + 1 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.y);
+                        if (r + 2 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.z);
+                    }
+                }
             }
         }
         total += h32;
+        if (!next) batch++;
     }
     return total;
 }
@@ -221,7 +252,7 @@ tc_warp_kernel(TcHeader *hdr, const int32_t *__restrict__ list, const int64_t *_
         if (idx >= nlist) break;
         const int64_t i = list[idx];
         tc_fill<TC_WARP_TAB, TC_WARP_BLOOM>(s_tab[w], s_bloom[w], mcrd, mpos[i], mpos[i + 1], lane, 32, false);
-        hits += tc_stream_rows<TC_WARP_TAB, TC_WARP_BLOOM>(s_tab[w], s_bloom[w], apos[i], apos[i + 1], 0, 1,
+        hits += tc_stream_rows<TC_WARP_TAB, TC_WARP_BLOOM>(s_tab[w], s_bloom[w], apos[i], apos[i + 1], nullptr,
                                                            lane, acrd, bpos, bcrd);
         __syncwarp();
     }
@@ -249,7 +280,7 @@ tc_block_kernel(TcHeader *hdr, int which, const int32_t *__restrict__ list,
 {
     extern __shared__ int32_t s_dyn_tc[];
     __shared__ unsigned long long s_part[THREADS / 32];
-    __shared__ unsigned s_idx;
+    __shared__ unsigned s_idx, s_batch;
     int32_t *tab = s_dyn_tc;
     uint32_t *bloom = (uint32_t *)(s_dyn_tc + (1 << LOG2));
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -277,8 +308,9 @@ tc_block_kernel(TcHeader *hdr, int which, const int32_t *__restrict__ list,
         }
         for (int64_t seg = ms; seg < me; seg += SEG) {
             const int64_t seg_end = seg + SEG < me ? seg + SEG : me;
+            if (threadIdx.x == 0) s_batch = 0;
             tc_fill<LOG2, BLOOM>(tab, bloom, mcrd, seg, seg_end, threadIdx.x, THREADS, true);
-            hits += tc_stream_rows<LOG2, BLOOM>(tab, bloom, as, ae, w, THREADS / 32, lane, acrd, bpos, bcrd);
+            hits += tc_stream_rows<LOG2, BLOOM>(tab, bloom, as, ae, &s_batch, lane, acrd, bpos, bcrd);
             __syncthreads();
         }
     }
