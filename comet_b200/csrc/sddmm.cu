@@ -17,8 +17,9 @@
 namespace cb200 {
 
 static const int SDDMM_THREADS = 256;
-static const int64_t SDDMM_LONG_ROW = 1024;
-static const int64_t SDDMM_CHUNK = 512;
+static const int64_t SDDMM_LONG_ROW = 256;
+static const int64_t SDDMM_CHUNK = 256;
+static const int SDDMM_BLOCK_ROWS = 8;     // consecutive rows a warp draws at a time (power of two <= 32)
 
 // Entries [s, e) of row `row`; xr holds this lane's part of X[row,:].
 template <int G, int NI>
@@ -76,6 +77,77 @@ __device__ __forceinline__ void load_x(double2 (&xr)[NI], const double *__restri
         xr[i] = (l + i * G < k2) ? __ldg(xp + l + i * G) : make_double2(0.0, 0.0);
 }
 
+// Entries [a, b) of a run of consecutive rows, as one stream: a batch of 32
+// consecutive entries may span several rows, so each entry carries its row
+// (found once per batch by a shuffle binary search over the 32 row pointers the
+// lanes hold) and X[row,:] is read through L1 next to Y[col,:].  The next
+// batch's coordinates and rows are fetched before the current batch is worked
+// on, so no load depends on another one inside the loop.
+template <int G, int NI>
+__device__ __forceinline__ void sample_stream(int64_t row0, int64_t rp, const int64_t *__restrict__ crd,
+                                              const double *__restrict__ sval,
+                                              const double *__restrict__ x, int64_t ldx,
+                                              const double *__restrict__ y, int64_t ldy,
+                                              double *__restrict__ out, int64_t a, int64_t b, int lane,
+                                              int k2)
+{
+    constexpr int P = 32 / G;
+    const int g = lane / G, l = lane % G;
+    auto fetch = [&](int64_t base, int64_t &c, int &row) {
+        const int64_t p = base + lane;
+        c = 0;
+        if (p < b) c = ld_stream(crd + p);
+        // last t in [0, BLOCK_ROWS) with pos[row0 + t] <= p  (rp = this lane's row pointer)
+        int lo = 0;
+#pragma unroll
+        for (int step = SDDMM_BLOCK_ROWS / 2; step > 0; step >>= 1) {
+            const int64_t v = __shfl_sync(0xffffffffu, (long long)rp, lo + step);
+            if (v <= p) lo += step;
+        }
+        row = lo;
+    };
+    int64_t c_next;
+    int row_next;
+    fetch(a, c_next, row_next);
+    for (int64_t base = a; base < b; base += 32) {
+        const int64_t c = c_next;
+        const int row = row_next;
+        if (base + 32 < b) fetch(base + 32, c_next, row_next);
+        const int n = (b - base) < 32 ? (int)(b - base) : 32;
+        const int steps = (n + P - 1) / P;
+        double mine = 0.0;
+#pragma unroll 2
+        for (int t = 0; t < steps; t++) {
+            const int idx = t * P + g;
+            const int64_t cc = __shfl_sync(0xffffffffu, (long long)c, idx & 31);
+            const int rr = __shfl_sync(0xffffffffu, row, idx & 31);
+            double d0 = 0.0, d1 = 0.0;
+            if (idx < n) {
+                const double2 *yr = (const double2 *)(y + cc * ldy);
+                const double2 *xp = (const double2 *)(x + (row0 + rr) * ldx);
+#pragma unroll
+                for (int i = 0; i < NI; i++) {
+                    if (l + i * G < k2) {
+                        const double2 yy = __ldg(yr + l + i * G);
+                        const double2 xx = __ldg(xp + l + i * G);
+                        d0 = fma(xx.x, yy.x, d0);
+                        d1 = fma(xx.y, yy.y, d1);
+                    }
+                }
+            }
+            double d = d0 + d1;
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            if (l == t) mine = d;
+        }
+        const int idx = l * P + g;
+        if (idx < n) out[base + idx] = ld_stream(sval + base + idx) * mine;
+    }
+}
+
+// Warps draw blocks of SDDMM_BLOCK_ROWS consecutive rows from a counter and walk each block's
+// entries as a stream; rows longer than LONG_ROW are cut out of the stream and
+// go to the chunk list.
 template <int G, int NI>
 __global__ void __launch_bounds__(SDDMM_THREADS)
 sddmm_rows_kernel(int64_t nrows, const int64_t *__restrict__ pos, const int64_t *__restrict__ crd,
@@ -85,29 +157,42 @@ sddmm_rows_kernel(int64_t nrows, const int64_t *__restrict__ pos, const int64_t 
 {
     const int lane = threadIdx.x & 31;
     const int k2 = k / 2;
-    const int64_t warp = ((int64_t)blockIdx.x * SDDMM_THREADS + threadIdx.x) >> 5;
-    const int64_t nwarps = ((int64_t)gridDim.x * SDDMM_THREADS) >> 5;
-    for (int64_t r = warp; r < nrows; r += nwarps) {
-        const int64_t s = pos[r], e = pos[r + 1];
-        if (s == e) continue;
-        if (e - s > SDDMM_LONG_ROW) {
-            if (lane == 0) {
-                unsigned n = (unsigned)((e - s + SDDMM_CHUNK - 1) / SDDMM_CHUNK);
-                unsigned at = atomicAdd(&hdr->count, n);
-                if (at + n <= chunk_cap) {
-                    for (unsigned i = 0; i < n; i++) {
-                        chunks[at + i].row = r;
-                        chunks[at + i].begin = s + (int64_t)i * SDDMM_CHUNK;
-                    }
-                } else {
-                    hdr->overflow = 1;
+    const int64_t nblocks = (nrows + SDDMM_BLOCK_ROWS - 1) / SDDMM_BLOCK_ROWS;
+    while (true) {
+        unsigned blk = 0;
+        if (lane == 0) blk = atomicAdd(&hdr->pad[0], 1u);
+        blk = __shfl_sync(0xffffffffu, blk, 0);
+        if ((int64_t)blk >= nblocks) break;
+        const int64_t row0 = (int64_t)blk * SDDMM_BLOCK_ROWS;
+        const int nr = (nrows - row0) < SDDMM_BLOCK_ROWS ? (int)(nrows - row0) : SDDMM_BLOCK_ROWS;
+        const int64_t rp = pos[row0 + (lane < nr ? lane : nr)];      // lanes past the block hold its end
+        const int64_t rnext = pos[row0 + (lane < nr ? lane + 1 : nr)];
+        const bool is_long = lane < nr && (rnext - rp) > SDDMM_LONG_ROW;
+        if (is_long) {
+            unsigned n = (unsigned)((rnext - rp + SDDMM_CHUNK - 1) / SDDMM_CHUNK);
+            unsigned at = atomicAdd(&hdr->count, n);
+            if (at + n <= chunk_cap) {
+                for (unsigned i = 0; i < n; i++) {
+                    chunks[at + i].row = row0 + lane;
+                    chunks[at + i].begin = rp + (int64_t)i * SDDMM_CHUNK;
                 }
+            } else {
+                hdr->overflow = 1;
             }
-            continue;
         }
-        double2 xr[NI];
-        load_x<G, NI>(xr, x, ldx, r, lane % G, k2);
-        sample_range<G, NI>(xr, crd, sval, y, ldy, out, s, e, lane, k2);
+        const unsigned longmask = __ballot_sync(0xffffffffu, is_long);
+        int t0 = 0;
+        while (t0 < nr) {
+            const unsigned m = longmask >> t0;
+            const int run = m ? (__ffs(m) - 1) : (nr - t0);      // rows [t0, t0 + run) hold no long row
+            if (run > 0) {
+                const int64_t a = __shfl_sync(0xffffffffu, (long long)rp, t0);
+                const int last = t0 + run - 1;
+                const int64_t b = __shfl_sync(0xffffffffu, (long long)rnext, last);
+                if (b > a) sample_stream<G, NI>(row0, rp, crd, sval, x, ldx, y, ldy, out, a, b, lane, k2);
+            }
+            t0 += run + 1;
+        }
     }
 }
 
