@@ -17,8 +17,8 @@
 namespace cb200 {
 
 static const int SDDMM_THREADS = 256;
-static const int64_t SDDMM_LONG_ROW = 256;
-static const int64_t SDDMM_CHUNK = 256;
+static const int64_t SDDMM_LONG_ROW = 32;
+static const int64_t SDDMM_CHUNK = 64;
 static const int SDDMM_BLOCK_ROWS = 8;     // consecutive rows a warp draws at a time (power of two <= 32)
 
 // Entries [s, e) of row `row`; xr holds this lane's part of X[row,:].
