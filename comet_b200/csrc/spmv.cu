@@ -12,7 +12,7 @@
 namespace cb200 {
 
 static const int SPMV_THREADS = 256;
-static const int SPMV_PASSES = 4;          // rows per lane group per CTA
+static const int SPMV_PASSES = 4;          // most rows per lane group per CTA (fewer on small matrices)
 static const int64_t LONG_ROW = 2048;
 
 template <bool PAIR>
@@ -53,7 +53,7 @@ template <int T, bool PAIR, bool VEC>
 __global__ void __launch_bounds__(SPMV_THREADS)
 spmv_kernel(int64_t nrows, const int64_t *__restrict__ row_ids, const int64_t *__restrict__ pos,
             const int64_t *__restrict__ crd, const double *__restrict__ val,
-            const double *__restrict__ x, double *__restrict__ y, int accumulate)
+            const double *__restrict__ x, double *__restrict__ y, int accumulate, int passes)
 {
     constexpr int GROUPS = SPMV_THREADS / T;
     constexpr int ROWS = GROUPS * SPMV_PASSES;
@@ -67,8 +67,8 @@ spmv_kernel(int64_t nrows, const int64_t *__restrict__ row_ids, const int64_t *_
     if (threadIdx.x == 0) n_long = 0;
     __syncthreads();
 
-    const int64_t row0 = (int64_t)blockIdx.x * ROWS;
-    for (int pass = 0; pass < SPMV_PASSES; pass++) {
+    const int64_t row0 = (int64_t)blockIdx.x * (GROUPS * passes);
+    for (int pass = 0; pass < passes; pass++) {
         int64_t r = row0 + pass * GROUPS + g;
         if (r >= nrows) break;
         int64_t s = pos[r], e = pos[r + 1];
@@ -108,9 +108,12 @@ static int launch_spmv(int64_t nrows, const int64_t *row_ids, const int64_t *pos
                        const double *val, const double *x, double *y, bool pair, bool vec,
                        int accumulate, cudaStream_t st)
 {
-    constexpr int ROWS = (SPMV_THREADS / T) * SPMV_PASSES;
-    unsigned grid = (unsigned)ceil_div(nrows, ROWS);
-#define GO(P, V) spmv_kernel<T, P, V><<<grid, SPMV_THREADS, 0, st>>>(nrows, row_ids, pos, crd, val, x, y, accumulate)
+    // small matrices: fewer rows per CTA so that the grid still covers every SM a few times
+    constexpr int GROUPS = SPMV_THREADS / T;
+    int passes = SPMV_PASSES;
+    while (passes > 1 && ceil_div(nrows, (int64_t)GROUPS * passes) < (int64_t)sm_count() * 4) passes--;
+    unsigned grid = (unsigned)ceil_div(nrows, (int64_t)GROUPS * passes);
+#define GO(P, V) spmv_kernel<T, P, V><<<grid, SPMV_THREADS, 0, st>>>(nrows, row_ids, pos, crd, val, x, y, accumulate, passes)
     if (pair) { if (vec) GO(true, true); else GO(true, false); }
     else      { if (vec) GO(false, true); else GO(false, false); }
 #undef GO
