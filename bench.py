@@ -33,6 +33,11 @@ if ROOT not in sys.path:
 
 FALLBACK_HBM_GBS = 6650.0
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one step's kernels at the default (full) size on one
+# GPU, from the one-pass ncu captures summarised under profiles/.  Reported as roofline.traffic only
+# when the run uses exactly that workload.
+NCU_DRAM_BYTES_PER_STEP = {"spmm": 6.144e9, "sddmm": 0.488e9, "spgemm": 77.2e9, "triangles": 25.2e9}
+
 
 def measured_peak():
     try:
@@ -141,7 +146,9 @@ class SpMM(Workload):
             scale, self.A.nnz, self.A.ncols, self.k)
         self.flops = 2.0 * self.A.nnz * self.k
         self.bytes = datasets.algorithmic_bytes("spmm", self.A.nrows, self.A.ncols, self.A.nnz, k=self.k)
-        self.weights = None
+        # work of a row block: one gathered B row per stored entry plus one written C row (and its
+        # row pointer) per row, so blocks are balanced on entries + 2 * rows rather than entries alone
+        self.weights = np.diff(self.A.a2pos) + 2
 
     def to_device(self, block, torch, dev):
         self.dA = dev.to_device(block)
@@ -267,7 +274,7 @@ class SDDMM(SpMM):
             scale, self.A.nnz, self.k)
         self.flops = float(self.A.nnz) * (2 * self.k + 1)
         self.bytes = datasets.algorithmic_bytes("sddmm", self.A.nrows, self.A.ncols, self.A.nnz, k=self.k)
-        self.weights = None
+        self.weights = np.diff(self.A.a2pos) + 1      # one gathered Y row per entry, one X row per row
 
     def to_device(self, block, torch, dev):
         self.dA = dev.to_device(block)
@@ -607,7 +614,11 @@ def main():
         "gpu_launches": w.launches_per_step * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "frac": achieved / peak,
+                     "traffic": (NCU_DRAM_BYTES_PER_STEP.get(w.name) if world == 1 and not args.scale
+                                 and not args.k and not args.variant else None),
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/",
+                     "peak_kind": peak_kind,
                      "algorithmic_bytes_per_step": int(rank_bytes), "kernel_ms_per_step": kernel_ms},
     }
     if not args.no_cpu and world == 1:
