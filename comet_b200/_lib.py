@@ -58,6 +58,10 @@ SIGNATURES = {
     "comet_b200_dev_masked_spgemm_count_f64_i64": (c_int32, [c_int64] * 6 + [c_void_p] * 7 + [c_void_p]),
 }
 
+# the host entry points exist once per index width
+for _name in [n for n in SIGNATURES if n.endswith("_f64_i64") and "_dev_" not in n]:
+    SIGNATURES[_name[:-4] + "_i32"] = SIGNATURES[_name]
+
 _lib = None
 
 

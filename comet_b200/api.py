@@ -4,8 +4,8 @@ memref descriptors, the same calls a COMET lowering would emit).
 
 Operands are packed the way cometpy packs them for ``_mlir_ciface_`` calls
 (frontends/numpy-scipy/cometpy/MLIRGen/lowering.py:283-360): a dims array, then
-per dimension pos / crd arrays, then values; index arrays are int64 and values
-float64.  Sparse operands may be
+per dimension pos / crd arrays, then values; values are float64, index arrays
+int64 or int32 (scipy's default), which selects the _i64 or _i32 entry points.  Sparse operands may be
 
   * any object with ``format`` ('CSR' | 'DCSR' | 'COO'), ``nrows``, ``ncols`` and
     the COMET arrays ``a1pos, a1crd, a2pos, a2crd, val`` (what COMET's reader
@@ -50,6 +50,16 @@ class SparseTensor:
     def shape(self):
         return (self.nrows, self.ncols)
 
+    @property
+    def index_dtype(self):
+        return np.asarray(self.a2crd).dtype
+
+    def with_index_dtype(self, dt):
+        if self.index_dtype == dt:
+            return self
+        return SparseTensor(self.format, self.nrows, self.ncols, _idx(self.a1pos, dt), _idx(self.a1crd, dt),
+                            _idx(self.a2pos, dt), _idx(self.a2crd, dt), self.val)
+
     def to_scipy(self):
         import scipy.sparse as sp
         if self.format == "CSR":
@@ -63,24 +73,38 @@ def _i64(a):
     return np.ascontiguousarray(a, dtype=np.int64)
 
 
+def _idx(a, dtype):
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+def _index_dtype(*arrays):
+    """int32 when every index array is int32 (scipy's default), else int64 -- the
+    rule cometpy applies to pick the index type of a sparse tensor
+    (frontends/numpy-scipy/cometpy/comet.py:198-218)."""
+    return np.int32 if all(np.asarray(a).dtype == np.int32 for a in arrays) else np.int64
+
+
 def _f64(a):
     return np.ascontiguousarray(a, dtype=np.float64)
 
 
 def as_sparse(m):
-    """scipy CSR/COO or a COMET-array object -> SparseTensor with int64/float64 arrays."""
+    """scipy CSR/COO or a COMET-array object -> SparseTensor (index width kept, values float64)."""
     if isinstance(m, SparseTensor):
         return m
     if hasattr(m, "a2crd") and hasattr(m, "format") and isinstance(m.format, str) and m.format.isupper():
-        return SparseTensor(m.format, m.nrows, m.ncols, _i64(m.a1pos), _i64(m.a1crd), _i64(m.a2pos),
-                            _i64(m.a2crd), _f64(m.val))
+        dt = _index_dtype(m.a1pos, m.a1crd, m.a2pos, m.a2crd)
+        return SparseTensor(m.format, m.nrows, m.ncols, _idx(m.a1pos, dt), _idx(m.a1crd, dt), _idx(m.a2pos, dt),
+                            _idx(m.a2crd, dt), _f64(m.val))
     fmt = getattr(m, "format", None)
     if fmt == "csr":
-        return SparseTensor("CSR", m.shape[0], m.shape[1], np.array([m.shape[0]], dtype=np.int64),
-                            np.array([-1], dtype=np.int64), _i64(m.indptr), _i64(m.indices), _f64(m.data))
+        dt = _index_dtype(m.indptr, m.indices)
+        return SparseTensor("CSR", m.shape[0], m.shape[1], np.array([m.shape[0]], dtype=dt),
+                            np.array([-1], dtype=dt), _idx(m.indptr, dt), _idx(m.indices, dt), _f64(m.data))
     if fmt == "coo":
-        return SparseTensor("COO", m.shape[0], m.shape[1], np.array([0, m.nnz], dtype=np.int64),
-                            _i64(m.row), np.array([-1], dtype=np.int64), _i64(m.col), _f64(m.data))
+        dt = _index_dtype(m.row, m.col)
+        return SparseTensor("COO", m.shape[0], m.shape[1], np.array([0, m.nnz], dtype=dt),
+                            _idx(m.row, dt), np.array([-1], dtype=dt), _idx(m.col, dt), _f64(m.data))
     raise TypeError("unsupported sparse operand: %r (CSR and COO are accepted, like cometpy)" % type(m))
 
 
@@ -115,13 +139,21 @@ class _Packer:
 
     def sparse(self, t):
         f1, f2 = _FMT[t.format]
-        empty = np.zeros(0, dtype=np.int64)
+        empty = np.zeros(0, dtype=t.index_dtype)
         dims = np.array([t.nrows, t.ncols], dtype=np.int64)
         args = [f1, -1, f2, -1]
         args += self.m1(t.a1pos) + self.m1(t.a1crd) + self.m1(empty) + self.m1(empty)
         args += self.m1(t.a2pos) + self.m1(t.a2crd) + self.m1(empty) + self.m1(empty)
         args += self.m1(t.val) + self.m1(dims)
         return args
+
+
+def _entry(lib, name, *tensors):
+    """The entry point of the operands' common index width, and the operands converted to it
+    (mixed widths are promoted to int64, like cometpy does)."""
+    dt = np.int32 if all(t.index_dtype == np.int32 for t in tensors) else np.int64
+    fn = getattr(lib, "comet_b200_%s_f64_%s" % (name, "i32" if dt == np.int32 else "i64"))
+    return fn, dt, [t.with_index_dtype(dt) for t in tensors]
 
 
 def _semiring(s):
@@ -140,8 +172,8 @@ def spmv(A, x, y0=None, semiring=PLUS_TIMES):
     pk = _Packer()
     x = _f64(x)
     y = np.zeros(A.nrows) if y0 is None else _f64(y0).copy()
-    lib.comet_b200_spmv_f64_i64(*pk.sparse(A), *pk.m1(x), *pk.m1(y), _semiring(semiring),
-                                0 if y0 is None else 1)
+    fn, _, (A,) = _entry(lib, "spmv", A)
+    fn(*pk.sparse(A), *pk.m1(x), *pk.m1(y), _semiring(semiring), 0 if y0 is None else 1)
     _lib.check()
     return y
 
@@ -153,8 +185,8 @@ def spmm(A, B, C0=None, semiring=PLUS_TIMES):
     pk = _Packer()
     B = _f64(B)
     C = np.zeros((A.nrows, B.shape[1])) if C0 is None else _f64(C0).copy()
-    lib.comet_b200_spmm_f64_i64(*pk.sparse(A), *pk.m2(B), *pk.m2(C), _semiring(semiring),
-                                0 if C0 is None else 1)
+    fn, _, (A,) = _entry(lib, "spmm", A)
+    fn(*pk.sparse(A), *pk.m2(B), *pk.m2(C), _semiring(semiring), 0 if C0 is None else 1)
     _lib.check()
     return C
 
@@ -169,7 +201,8 @@ def sddmm(S, X, Y, y_is_kj=False):
     out = SparseTensor("CSR", S.nrows, S.ncols, np.zeros_like(S.a1pos), np.zeros_like(S.a1crd),
                        np.zeros_like(S.a2pos), np.zeros_like(S.a2crd), np.zeros(S.nnz))
     d_args = pk.m2(Y) if y_is_kj else pk.m2(Y, transposed_view=True)
-    lib.comet_b200_sddmm_f64_i64(*pk.sparse(S), *pk.m2(X), *d_args, *pk.sparse(out))
+    fn, _, _unused = _entry(lib, "sddmm", S)
+    fn(*pk.sparse(S), *pk.m2(X), *d_args, *pk.sparse(out))
     _lib.check()
     assert np.array_equal(out.a2pos, S.a2pos) and np.array_equal(out.a2crd, S.a2crd)
     return out.val
@@ -183,7 +216,8 @@ def elews_sparse_dense(A, B):
     B = _f64(B)
     out = SparseTensor(A.format, A.nrows, A.ncols, np.zeros_like(A.a1pos), np.zeros_like(A.a1crd),
                        np.zeros_like(A.a2pos), np.zeros_like(A.a2crd), np.zeros(A.nnz))
-    lib.comet_b200_elews_mul_sparse_dense_f64_i64(*pk.sparse(A), *pk.m2(B), *pk.sparse(out))
+    fn, _, _unused = _entry(lib, "elews_mul_sparse_dense", A)
+    fn(*pk.sparse(A), *pk.m2(B), *pk.sparse(out))
     _lib.check()
     return out.val
 
@@ -191,13 +225,15 @@ def elews_sparse_dense(A, B):
 def _finish_sparse_out(lib, handle, nrows, ncols, cpos, sizes):
     _lib.check()
     nnz = int(sizes[8])
-    ccrd = np.zeros(nnz, dtype=np.int64)
+    dt = cpos.dtype
+    ccrd = np.zeros(nnz, dtype=dt)
     cval = np.zeros(nnz, dtype=np.float64)
     pk = _Packer()
-    lib.comet_b200_spgemm_numeric_f64_i64(handle, *pk.m1(ccrd), *pk.m1(cval))
+    fn = lib.comet_b200_spgemm_numeric_f64_i32 if dt == np.int32 else lib.comet_b200_spgemm_numeric_f64_i64
+    fn(handle, *pk.m1(ccrd), *pk.m1(cval))
     _lib.check()
-    return SparseTensor("CSR", nrows, ncols, np.array([nrows], dtype=np.int64),
-                        np.array([-1], dtype=np.int64), cpos, ccrd, cval)
+    return SparseTensor("CSR", nrows, ncols, np.array([nrows], dtype=dt), np.array([-1], dtype=dt), cpos, ccrd,
+                        cval)
 
 
 def spgemm(A, B, M=None, semiring=PLUS_TIMES):
@@ -206,11 +242,11 @@ def spgemm(A, B, M=None, semiring=PLUS_TIMES):
     Mt = as_sparse(M) if M is not None else A
     lib = _lib.load()
     pk = _Packer()
-    cpos = np.zeros(A.nrows + 1, dtype=np.int64)
+    fn, dt, (A, B, Mt) = _entry(lib, "spgemm_symbolic", A, B, Mt)
+    cpos = np.zeros(A.nrows + 1, dtype=dt)
     sizes = np.zeros(11, dtype=np.int64)
-    handle = lib.comet_b200_spgemm_symbolic_f64_i64(
-        *pk.sparse(A), *pk.sparse(B), *pk.sparse(Mt), MASK_PUSH if M is not None else MASK_NONE,
-        _semiring(semiring), *pk.m1(cpos), *pk.m1(sizes))
+    handle = fn(*pk.sparse(A), *pk.sparse(B), *pk.sparse(Mt), MASK_PUSH if M is not None else MASK_NONE,
+                _semiring(semiring), *pk.m1(cpos), *pk.m1(sizes))
     return _finish_sparse_out(lib, handle, A.nrows, B.ncols, cpos, sizes)
 
 
@@ -219,10 +255,10 @@ def elews_csr_csr(A, B):
     A, B = as_sparse(A), as_sparse(B)
     lib = _lib.load()
     pk = _Packer()
-    cpos = np.zeros(A.nrows + 1, dtype=np.int64)
+    fn, dt, (A, B) = _entry(lib, "elews_mul_sparse_sparse_symbolic", A, B)
+    cpos = np.zeros(A.nrows + 1, dtype=dt)
     sizes = np.zeros(11, dtype=np.int64)
-    handle = lib.comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64(
-        *pk.sparse(A), *pk.sparse(B), *pk.m1(cpos), *pk.m1(sizes))
+    handle = fn(*pk.sparse(A), *pk.sparse(B), *pk.m1(cpos), *pk.m1(sizes))
     return _finish_sparse_out(lib, handle, A.nrows, A.ncols, cpos, sizes)
 
 
@@ -232,8 +268,8 @@ def masked_pair_count(A, B, M):
     lib = _lib.load()
     pk = _Packer()
     out = np.zeros(1, dtype=np.int64)
-    lib.comet_b200_masked_spgemm_count_f64_i64(*pk.sparse(A), *pk.sparse(B), *pk.sparse(M), MASK_PUSH,
-                                               PLUS_PAIR, *pk.m1(out))
+    fn, _, (A, B, M) = _entry(lib, "masked_spgemm_count", A, B, M)
+    fn(*pk.sparse(A), *pk.sparse(B), *pk.sparse(M), MASK_PUSH, PLUS_PAIR, *pk.m1(out))
     _lib.check()
     return int(out[0])
 

@@ -59,50 +59,62 @@ enum { F_CSR, F_DCSR, F_COO };
 
 struct HostSparse {
     int fmt;
+    int isz;                              // bytes per index: 8 (_i64 entry points) or 4 (_i32)
     int64_t nrows, ncols, nnz, nstored;   // nstored: rows held (DCSR), else nrows
-    int64_t *a1pos, *a1crd, *a2pos, *a2crd;
+    char *a1pos, *a1crd, *a2pos, *a2crd;  // index arrays of `isz`-byte integers
     double *val;
 };
+
+static inline int64_t idx_get(const char *p, int64_t i, int isz)
+{
+    return isz == 8 ? ((const int64_t *)p)[i] : (int64_t)((const int32_t *)p)[i];
+}
+
+static inline void idx_set(char *p, int64_t i, int isz, int64_t v)
+{
+    if (isz == 8) ((int64_t *)p)[i] = v; else ((int32_t *)p)[i] = (int32_t)v;
+}
 
 #define SPARSE_ARGS(P) P##1format, P##2format, P##1pos_rank, P##1pos_ptr, P##1crd_rank, P##1crd_ptr, \
     P##2pos_rank, P##2pos_ptr, P##2crd_rank, P##2crd_ptr, P##val_rank, P##val_ptr, P##dims_rank, P##dims_ptr
 
-static int get_sparse(const char *what, int32_t f1, int32_t f2, int64_t r1p, void *p1p, int64_t r1c,
+static int get_sparse(const char *what, int isz, int32_t f1, int32_t f2, int64_t r1p, void *p1p, int64_t r1c,
                       void *p1c, int64_t r2p, void *p2p, int64_t r2c, void *p2c, int64_t rv, void *pv,
                       int64_t rd, void *pd, HostSparse *s)
 {
     Arr a1pos, a1crd, a2pos, a2crd, val, dims;
-    CB_TRY(get1d(what, r1p, p1p, 8, &a1pos));
-    CB_TRY(get1d(what, r1c, p1c, 8, &a1crd));
-    CB_TRY(get1d(what, r2p, p2p, 8, &a2pos));
-    CB_TRY(get1d(what, r2c, p2c, 8, &a2crd));
+    s->isz = isz;
+    CB_TRY(get1d(what, r1p, p1p, isz, &a1pos));
+    CB_TRY(get1d(what, r1c, p1c, isz, &a1crd));
+    CB_TRY(get1d(what, r2p, p2p, isz, &a2pos));
+    CB_TRY(get1d(what, r2c, p2c, isz, &a2crd));
     CB_TRY(get1d(what, rv, pv, 8, &val));
     CB_TRY(get1d(what, rd, pd, 8, &dims));
     if (dims.n < 2 || !dims.data) return fail("%s: dims memref must hold {rows, cols}", what);
     s->nrows = ((int64_t *)dims.data)[0];
     s->ncols = ((int64_t *)dims.data)[1];
     if (s->nrows < 0 || s->ncols < 0) return fail("%s: negative dimension", what);
-    s->a1pos = (int64_t *)a1pos.data; s->a1crd = (int64_t *)a1crd.data;
-    s->a2pos = (int64_t *)a2pos.data; s->a2crd = (int64_t *)a2crd.data;
+    s->a1pos = (char *)a1pos.data; s->a1crd = (char *)a1crd.data;
+    s->a2pos = (char *)a2pos.data; s->a2crd = (char *)a2crd.data;
     s->val = (double *)val.data;
     if (f1 == COMET_B200_FMT_DENSE && f2 == COMET_B200_FMT_CU) {
         s->fmt = F_CSR;
         if (a2pos.n < s->nrows + 1) return fail("%s: CSR pos array shorter than rows+1", what);
         s->nstored = s->nrows;
-        s->nnz = s->nrows > 0 ? s->a2pos[s->nrows] : 0;
+        s->nnz = s->nrows > 0 ? idx_get(s->a2pos, s->nrows, isz) : 0;
     } else if (f1 == COMET_B200_FMT_CU && f2 == COMET_B200_FMT_CU) {
         s->fmt = F_DCSR;
         if (a1pos.n < 2) return fail("%s: DCSR A1pos must hold {0, stored rows}", what);
-        s->nstored = s->a1pos[1] - s->a1pos[0];
-        if (s->a1pos[0] != 0) return fail("%s: DCSR A1pos[0] must be 0", what);
+        s->nstored = idx_get(s->a1pos, 1, isz) - idx_get(s->a1pos, 0, isz);
+        if (idx_get(s->a1pos, 0, isz) != 0) return fail("%s: DCSR A1pos[0] must be 0", what);
         if (a1crd.n < s->nstored || a2pos.n < s->nstored + 1)
             return fail("%s: DCSR arrays shorter than the stored row count", what);
-        s->nnz = s->nstored > 0 ? s->a2pos[s->nstored] : 0;
+        s->nnz = s->nstored > 0 ? idx_get(s->a2pos, s->nstored, isz) : 0;
     } else if (f1 == COMET_B200_FMT_CN && f2 == COMET_B200_FMT_S) {
         s->fmt = F_COO;
         if (a1pos.n < 2) return fail("%s: COO A1pos must hold {0, nnz}", what);
-        if (s->a1pos[0] != 0) return fail("%s: COO A1pos[0] must be 0", what);
-        s->nnz = s->a1pos[1];
+        if (idx_get(s->a1pos, 0, isz) != 0) return fail("%s: COO A1pos[0] must be 0", what);
+        s->nnz = idx_get(s->a1pos, 1, isz);
         s->nstored = s->nrows;
         if (a1crd.n < s->nnz) return fail("%s: COO row coordinates shorter than nnz", what);
     } else {
@@ -137,6 +149,15 @@ struct DevBag {
         if (bytes) CB_CUDA(cudaMemcpyAsync(*p, host, bytes, cudaMemcpyHostToDevice, st));
         return 0;
     }
+    // n indices of isz bytes -> int64 on the device (int32 input is widened there, not on the host)
+    int upload_idx(int64_t **p, const void *host, int64_t n, int isz)
+    {
+        if (isz == 8) return upload((void **)p, host, (size_t)n * 8);
+        void *narrow = nullptr;
+        CB_TRY(upload(&narrow, host, (size_t)n * 4));
+        CB_TRY(alloc((void **)p, (size_t)n * 8));
+        return widen_i32_to_i64((const int32_t *)narrow, *p, n, st);
+    }
 };
 
 struct DevSparse {
@@ -167,18 +188,18 @@ static int upload_sparse(const char *what, const HostSparse &h, DevBag &bag, Dev
 {
     memset(d, 0, sizeof(*d));
     cudaStream_t st = bag.st;
-    CB_TRY(bag.upload((void **)&d->crd, h.a2crd, (size_t)h.nnz * 8));
+    CB_TRY(bag.upload_idx(&d->crd, h.a2crd, h.nnz, h.isz));
     if (need_val) CB_TRY(bag.upload((void **)&d->val, h.val, (size_t)h.nnz * 8));
     if (h.fmt == F_CSR) {
         d->nrows_k = h.nrows;
-        CB_TRY(bag.upload((void **)&d->pos, h.a2pos, (size_t)(h.nrows + 1) * 8));
+        CB_TRY(bag.upload_idx(&d->pos, h.a2pos, h.nrows + 1, h.isz));
     } else if (h.fmt == F_DCSR) {
         d->nrows_k = h.nstored;
-        CB_TRY(bag.upload((void **)&d->pos, h.a2pos, (size_t)(h.nstored + 1) * 8));
-        CB_TRY(bag.upload((void **)&d->row_ids, h.a1crd, (size_t)h.nstored * 8));
+        CB_TRY(bag.upload_idx(&d->pos, h.a2pos, h.nstored + 1, h.isz));
+        CB_TRY(bag.upload_idx(&d->row_ids, h.a1crd, h.nstored, h.isz));
     } else {
         d->nrows_k = h.nrows;
-        CB_TRY(bag.upload((void **)&d->rows, h.a1crd, (size_t)h.nnz * 8));
+        CB_TRY(bag.upload_idx(&d->rows, h.a1crd, h.nnz, h.isz));
         CB_TRY(bag.alloc((void **)&d->pos, (size_t)(h.nrows + 1) * 8));
         int *flag = nullptr;
         CB_TRY(bag.alloc((void **)&flag, sizeof(int)));
@@ -212,6 +233,7 @@ static int need_stream(cudaStream_t *st)
 
 // Handles created through the host layer also own their staged operands.
 struct HostPlan {
+    int isz;
     int64_t dev_handle;
     std::vector<void *> owned;
     int64_t nnz;
@@ -278,14 +300,15 @@ static void copy_pattern(const HostSparse &src, const HostSparse &dst)
 {
     // the output tensor shares the sparse operand's pos/crd
     // (lib/Conversion/IndexTreeToSCF/SymbolicDomainConversion.cpp:277-297)
+    const int isz = src.isz;
     if (src.fmt == F_CSR) {
-        if (dst.a1pos && dst.a1pos != src.a1pos) dst.a1pos[0] = src.nrows;
-        if (dst.a2pos != src.a2pos) memcpy(dst.a2pos, src.a2pos, (size_t)(src.nrows + 1) * 8);
+        if (dst.a1pos && dst.a1pos != src.a1pos) idx_set(dst.a1pos, 0, isz, src.nrows);
+        if (dst.a2pos != src.a2pos) memcpy(dst.a2pos, src.a2pos, (size_t)(src.nrows + 1) * isz);
     } else if (src.fmt == F_COO) {
-        if (dst.a1pos != src.a1pos) { dst.a1pos[0] = 0; dst.a1pos[1] = src.nnz; }
-        if (dst.a1crd != src.a1crd) memcpy(dst.a1crd, src.a1crd, (size_t)src.nnz * 8);
+        if (dst.a1pos != src.a1pos) { idx_set(dst.a1pos, 0, isz, 0); idx_set(dst.a1pos, 1, isz, src.nnz); }
+        if (dst.a1crd != src.a1crd) memcpy(dst.a1crd, src.a1crd, (size_t)src.nnz * isz);
     }
-    if (dst.a2crd != src.a2crd) memcpy(dst.a2crd, src.a2crd, (size_t)src.nnz * 8);
+    if (dst.a2crd != src.a2crd) memcpy(dst.a2crd, src.a2crd, (size_t)src.nnz * isz);
 }
 
 }  // namespace cb200
@@ -293,18 +316,22 @@ static void copy_pattern(const HostSparse &src, const HostSparse &dst)
 using namespace cb200;
 
 #define GET_SPARSE(name, P, hs) \
-    get_sparse(name, P##1format, P##2format, P##1pos_rank, P##1pos_ptr, P##1crd_rank, P##1crd_ptr, \
+    get_sparse(name, isz, P##1format, P##2format, P##1pos_rank, P##1pos_ptr, P##1crd_rank, P##1crd_ptr, \
                P##2pos_rank, P##2pos_ptr, P##2crd_rank, P##2crd_ptr, P##val_rank, P##val_ptr,       \
                P##dims_rank, P##dims_ptr, hs)
+
+// all 24 arguments of one sparse operand, for forwarding
+#define FWD_SPARSE(P) P##1format, P##1tile_format, P##2format, P##2tile_format, P##1pos_rank, P##1pos_ptr, \
+    P##1crd_rank, P##1crd_ptr, P##1tile_pos_rank, P##1tile_pos_ptr, P##1tile_crd_rank, P##1tile_crd_ptr,     \
+    P##2pos_rank, P##2pos_ptr, P##2crd_rank, P##2crd_ptr, P##2tile_pos_rank, P##2tile_pos_ptr,               \
+    P##2tile_crd_rank, P##2tile_crd_ptr, P##val_rank, P##val_ptr, P##dims_rank, P##dims_ptr
 
 #define UNUSED_TILES(P) (void)P##1tile_format; (void)P##2tile_format; (void)P##1tile_pos_rank; \
     (void)P##1tile_pos_ptr; (void)P##1tile_crd_rank; (void)P##1tile_crd_ptr; (void)P##2tile_pos_rank; \
     (void)P##2tile_pos_ptr; (void)P##2tile_crd_rank; (void)P##2tile_crd_ptr
 
-extern "C" {
-
-void comet_b200_spmv_f64_i64(COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr, int64_t y_rank,
-                             void *y_ptr, int32_t semiring, int32_t accumulate)
+static void spmv_impl(int isz, COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr, int64_t y_rank,
+                      void *y_ptr, int32_t semiring, int32_t accumulate)
 {
     UNUSED_TILES(A);
     clear_error();
@@ -315,8 +342,8 @@ void comet_b200_spmv_f64_i64(COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr
     spmv_host(A, x, y, semiring, accumulate);
 }
 
-void comet_b200_spmm_f64_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank,
-                             void *C_ptr, int32_t semiring, int32_t accumulate)
+static void spmm_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank,
+                      void *C_ptr, int32_t semiring, int32_t accumulate)
 {
     UNUSED_TILES(A);
     clear_error();
@@ -327,8 +354,8 @@ void comet_b200_spmm_f64_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr
     spmm_host(A, B, C, semiring, accumulate);
 }
 
-void comet_b200_sddmm_f64_i64(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank,
-                              void *D_ptr, COMET_B200_SPARSE2D(O))
+static void sddmm_impl(int isz, COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank,
+                       void *D_ptr, COMET_B200_SPARSE2D(O))
 {
     UNUSED_TILES(S);
     UNUSED_TILES(O);
@@ -373,8 +400,8 @@ void comet_b200_sddmm_f64_i64(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_pt
     finish(st);
 }
 
-void comet_b200_elews_mul_sparse_dense_f64_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
-                                               COMET_B200_SPARSE2D(C))
+static void elews_sd_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                          COMET_B200_SPARSE2D(C))
 {
     UNUSED_TILES(A);
     UNUSED_TILES(C);
@@ -390,10 +417,10 @@ void comet_b200_elews_mul_sparse_dense_f64_i64(COMET_B200_SPARSE2D(A), int64_t B
     DevBag bag(st);
     DevSparse dA;
     memset(&dA, 0, sizeof(dA));
-    if (bag.upload((void **)&dA.crd, A.a2crd, (size_t)A.nnz * 8)) return;
+    if (bag.upload_idx(&dA.crd, A.a2crd, A.nnz, A.isz)) return;
     if (bag.upload((void **)&dA.val, A.val, (size_t)A.nnz * 8)) return;
-    if (A.fmt == F_CSR) { if (bag.upload((void **)&dA.pos, A.a2pos, (size_t)(A.nrows + 1) * 8)) return; }
-    else { if (bag.upload((void **)&dA.rows, A.a1crd, (size_t)A.nnz * 8)) return; }
+    if (A.fmt == F_CSR) { if (bag.upload_idx(&dA.pos, A.a2pos, A.nrows + 1, A.isz)) return; }
+    else { if (bag.upload_idx(&dA.rows, A.a1crd, A.nnz, A.isz)) return; }
     double *dB, *dOut;
     if (bag.upload((void **)&dB, B.data, A.nrows > 0 ? (size_t)((A.nrows - 1) * B.s0 + A.ncols) * 8 : 0)) return;
     if (bag.alloc((void **)&dOut, (size_t)A.nnz * 8)) return;
@@ -408,7 +435,7 @@ void comet_b200_elews_mul_sparse_dense_f64_i64(COMET_B200_SPARSE2D(A), int64_t B
     finish(st);
 }
 
-static int64_t sparse_out_symbolic(int kind, const HostSparse &A, const HostSparse &B,
+static int64_t sparse_out_symbolic(int isz, int kind, const HostSparse &A, const HostSparse &B,
                                    const HostSparse *M, int semiring, Arr cpos, int64_t sizes_rank,
                                    void *sizes_ptr)
 {
@@ -444,7 +471,20 @@ static int64_t sparse_out_symbolic(int kind, const HostSparse &A, const HostSpar
         rc = comet_b200_dev_elews_mul_sparse_sparse_symbolic_f64_i64(
             A.nrows, dA.pos, dA.crd, dA.val, dB.pos, dB.crd, dB.val, dcpos, &nnz, &dev_handle, st);
     if (rc) return 0;
-    if (cudaMemcpyAsync(cpos.data, dcpos, (size_t)(A.nrows + 1) * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+    if (isz == 4 && nnz >= 0x7fffffffLL) {
+        comet_b200_handle_destroy(dev_handle);
+        return fail("sparse output: %lld entries do not fit 32-bit indices; use the _i64 entry point", (long long)nnz), 0;
+    }
+    void *pos_src = dcpos;
+    if (isz == 4) {     // narrow the row pointer on the device before it goes back
+        int32_t *p32;
+        if (bag.alloc((void **)&p32, (size_t)(A.nrows + 1) * 4) || narrow_any_i64_to_i32(dcpos, p32, A.nrows + 1, st)) {
+            comet_b200_handle_destroy(dev_handle);
+            return 0;
+        }
+        pos_src = p32;
+    }
+    if (cudaMemcpyAsync(cpos.data, pos_src, (size_t)(A.nrows + 1) * isz, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
         cudaStreamSynchronize(st) != cudaSuccess) {
         comet_b200_handle_destroy(dev_handle);
         return fail("sparse output: copy of C2pos failed"), 0;
@@ -453,16 +493,17 @@ static int64_t sparse_out_symbolic(int kind, const HostSparse &A, const HostSpar
     HostPlan *hp = new HostPlan();
     hp->dev_handle = dev_handle;
     hp->nnz = nnz;
+    hp->isz = isz;
     hp->owned.swap(bag.ptrs);   // staged operands live until the numeric call
     std::lock_guard<std::mutex> lk(g_hp_mu);
     g_hplans[dev_handle] = hp;
     return dev_handle;
 }
 
-int64_t comet_b200_spgemm_symbolic_f64_i64(COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
-                                           COMET_B200_SPARSE2D(M), int32_t mask_type,
-                                           int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr,
-                                           int64_t sizes_rank, void *sizes_ptr)
+static int64_t spgemm_symbolic_impl(int isz, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
+                                    COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
+                                    int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank,
+                                    void *sizes_ptr)
 {
     UNUSED_TILES(A);
     UNUSED_TILES(B);
@@ -477,14 +518,13 @@ int64_t comet_b200_spgemm_symbolic_f64_i64(COMET_B200_SPARSE2D(A), COMET_B200_SP
     }
     bool masked = mask_type == COMET_B200_MASK_PUSH;
     if (masked && GET_SPARSE("spgemm: M", M, &M)) return 0;
-    if (get1d("spgemm: C2pos", C2pos_rank, C2pos_ptr, 8, &cpos)) return 0;
-    return sparse_out_symbolic(0, A, B, masked ? &M : nullptr, semiring, cpos, sizes_rank, sizes_ptr);
+    if (get1d("spgemm: C2pos", C2pos_rank, C2pos_ptr, isz, &cpos)) return 0;
+    return sparse_out_symbolic(isz, 0, A, B, masked ? &M : nullptr, semiring, cpos, sizes_rank, sizes_ptr);
 }
 
-int64_t comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64(COMET_B200_SPARSE2D(A),
-                                                            COMET_B200_SPARSE2D(B),
-                                                            int64_t C2pos_rank, void *C2pos_ptr,
-                                                            int64_t sizes_rank, void *sizes_ptr)
+static int64_t elews_ss_symbolic_impl(int isz, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
+                                      int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank,
+                                      void *sizes_ptr)
 {
     UNUSED_TILES(A);
     UNUSED_TILES(B);
@@ -492,12 +532,12 @@ int64_t comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64(COMET_B200_SPARSE2D(
     HostSparse A, B;
     Arr cpos;
     if (GET_SPARSE("elews_mul: A", A, &A) || GET_SPARSE("elews_mul: B", B, &B)) return 0;
-    if (get1d("elews_mul: C2pos", C2pos_rank, C2pos_ptr, 8, &cpos)) return 0;
-    return sparse_out_symbolic(1, A, B, nullptr, COMET_B200_PLUS_TIMES, cpos, sizes_rank, sizes_ptr);
+    if (get1d("elews_mul: C2pos", C2pos_rank, C2pos_ptr, isz, &cpos)) return 0;
+    return sparse_out_symbolic(isz, 1, A, B, nullptr, COMET_B200_PLUS_TIMES, cpos, sizes_rank, sizes_ptr);
 }
 
-void comet_b200_spgemm_numeric_f64_i64(int64_t handle, int64_t C2crd_rank, void *C2crd_ptr,
-                                       int64_t Cval_rank, void *Cval_ptr)
+static void spgemm_numeric_impl(int isz, int64_t handle, int64_t C2crd_rank, void *C2crd_ptr,
+                                int64_t Cval_rank, void *Cval_ptr)
 {
     clear_error();
     HostPlan *hp = nullptr;
@@ -509,7 +549,8 @@ void comet_b200_spgemm_numeric_f64_i64(int64_t handle, int64_t C2crd_rank, void 
     if (!hp) { fail("numeric phase: unknown handle %lld", (long long)handle); return; }
     cudaStream_t st = lib_stream();
     Arr crd, val;
-    int rc = get1d("C2crd", C2crd_rank, C2crd_ptr, 8, &crd) || get1d("Cval", Cval_rank, Cval_ptr, 8, &val);
+    int rc = get1d("C2crd", C2crd_rank, C2crd_ptr, isz, &crd) || get1d("Cval", Cval_rank, Cval_ptr, 8, &val);
+    if (!rc && hp->isz != isz) rc = fail("numeric phase: the handle was created by the entry point of the other index width");
     if (!rc && (crd.n < hp->nnz || val.n < hp->nnz)) rc = fail("numeric phase: C2crd/Cval shorter than nnz");
     int64_t *dcrd = nullptr;
     double *dval = nullptr;
@@ -519,21 +560,29 @@ void comet_b200_spgemm_numeric_f64_i64(int64_t handle, int64_t C2crd_rank, void 
         rc = fail("numeric phase: device allocation failed");
     if (!rc) rc = comet_b200_dev_spgemm_numeric_f64_i64(hp->dev_handle, dcrd, dval, 0, st);
     else comet_b200_handle_destroy(hp->dev_handle);
+    int32_t *dcrd32 = nullptr;
+    if (!rc && hp->nnz && isz == 4) {
+        if (cudaMallocAsync((void **)&dcrd32, (size_t)hp->nnz * 4, st) != cudaSuccess)
+            rc = fail("numeric phase: device allocation failed");
+        if (!rc) rc = narrow_any_i64_to_i32(dcrd, dcrd32, hp->nnz, st);
+    }
     if (!rc && hp->nnz) {
-        if (cudaMemcpyAsync(crd.data, dcrd, (size_t)hp->nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        if (cudaMemcpyAsync(crd.data, isz == 4 ? (void *)dcrd32 : (void *)dcrd, (size_t)hp->nnz * isz,
+                            cudaMemcpyDeviceToHost, st) != cudaSuccess ||
             cudaMemcpyAsync(val.data, dval, (size_t)hp->nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess)
             rc = fail("numeric phase: copy of the result failed");
     }
     if (cudaStreamSynchronize(st) != cudaSuccess && !rc) fail("numeric phase: synchronize failed");
     if (dcrd) cudaFreeAsync(dcrd, st);
+    if (dcrd32) cudaFreeAsync(dcrd32, st);
     if (dval) cudaFreeAsync(dval, st);
     for (void *p : hp->owned) cudaFreeAsync(p, st);
     delete hp;
 }
 
-void comet_b200_masked_spgemm_count_f64_i64(COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
-                                            COMET_B200_SPARSE2D(M), int32_t mask_type,
-                                            int32_t semiring, int64_t out_rank, void *out_ptr)
+static void masked_count_impl(int isz, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
+                              COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
+                              int64_t out_rank, void *out_ptr)
 {
     UNUSED_TILES(A);
     UNUSED_TILES(B);
@@ -569,5 +618,49 @@ void comet_b200_masked_spgemm_count_f64_i64(COMET_B200_SPARSE2D(A), COMET_B200_S
     if (cudaMemcpyAsync(out.data, dcount, 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) { fail("masked count: copy failed"); return; }
     finish(st);
 }
+
+// ---------------------------------------------------------------------------
+// Exported symbols: one per index width.  COMET's CPU target uses i64 indices
+// (frontends/comet_dsl/comet.cpp:817-823); cometpy keeps scipy's int32 index
+// arrays and then instantiates the _i32 symbols
+// (frontends/numpy-scipy/cometpy/comet.py:198-218).  Narrow indices are widened
+// on the device, so both widths run the same kernels.
+// ---------------------------------------------------------------------------
+extern "C" {
+
+#define BOTH_WIDTHS(RET, NAME, IMPL, PARAMS, ...)                           \
+    RET comet_b200_##NAME##_f64_i64 PARAMS { return IMPL(8, __VA_ARGS__); } \
+    RET comet_b200_##NAME##_f64_i32 PARAMS { return IMPL(4, __VA_ARGS__); }
+
+BOTH_WIDTHS(void, spmv, spmv_impl,
+            (COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr, int64_t y_rank, void *y_ptr, int32_t semiring,
+             int32_t accumulate),
+            FWD_SPARSE(A), x_rank, x_ptr, y_rank, y_ptr, semiring, accumulate)
+BOTH_WIDTHS(void, spmm, spmm_impl,
+            (COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank, void *C_ptr, int32_t semiring,
+             int32_t accumulate),
+            FWD_SPARSE(A), B_rank, B_ptr, C_rank, C_ptr, semiring, accumulate)
+BOTH_WIDTHS(void, sddmm, sddmm_impl,
+            (COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O)),
+            FWD_SPARSE(S), X_rank, X_ptr, D_rank, D_ptr, FWD_SPARSE(O))
+BOTH_WIDTHS(void, elews_mul_sparse_dense, elews_sd_impl,
+            (COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, COMET_B200_SPARSE2D(C)),
+            FWD_SPARSE(A), B_rank, B_ptr, FWD_SPARSE(C))
+BOTH_WIDTHS(int64_t, spgemm_symbolic, spgemm_symbolic_impl,
+            (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
+             int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr),
+            FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, C2pos_rank ,
+                C2pos_ptr, sizes_rank, sizes_ptr)
+BOTH_WIDTHS(int64_t, elews_mul_sparse_sparse_symbolic, elews_ss_symbolic_impl,
+            (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank,
+             void *sizes_ptr),
+            FWD_SPARSE(A), FWD_SPARSE(B), C2pos_rank, C2pos_ptr, sizes_rank, sizes_ptr)
+BOTH_WIDTHS(void, spgemm_numeric, spgemm_numeric_impl,
+            (int64_t handle, int64_t C2crd_rank, void *C2crd_ptr, int64_t Cval_rank, void *Cval_ptr),
+            handle, C2crd_rank, C2crd_ptr, Cval_rank, Cval_ptr)
+BOTH_WIDTHS(void, masked_spgemm_count, masked_count_impl,
+            (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
+             int64_t out_rank, void *out_ptr),
+            FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, out_rank, out_ptr)
 
 }  // extern "C"

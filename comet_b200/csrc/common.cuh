@@ -64,6 +64,8 @@ cudaStream_t lib_stream();   // the library's own stream for the host-memref ent
 // Small shared kernels (util.cu)
 // ---------------------------------------------------------------------------
 int narrow_i64_to_i32(const int64_t *src, int32_t *dst, int64_t n, cudaStream_t st);
+int narrow_any_i64_to_i32(const int64_t *src, int32_t *dst, int64_t n, cudaStream_t st);
+int widen_i32_to_i64(const int32_t *src, int64_t *dst, int64_t n, cudaStream_t st);
 // out[0..n] = exclusive prefix sum of in[0..n-1], out[n] = total
 int exclusive_scan_i64(const int64_t *in, int64_t *out, int64_t n, cudaStream_t st);
 // sorted COO row coordinates -> row pointer; *sorted_flag_dev set to 0 if rows are not ascending

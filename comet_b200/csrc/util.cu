@@ -20,6 +20,46 @@ __global__ void __launch_bounds__(256) narrow_kernel(const int64_t *__restrict__
     }
 }
 
+__global__ void __launch_bounds__(256) widen_kernel(const int32_t *__restrict__ src,
+                                                    int64_t *__restrict__ dst, int64_t n)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = (int64_t)__ldcs(src + i);
+}
+
+__global__ void __launch_bounds__(256) narrow_scalar_kernel(const int64_t *__restrict__ src,
+                                                            int32_t *__restrict__ dst, int64_t n)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = (int32_t)src[i];
+}
+
+static unsigned stream_grid(int64_t n)
+{
+    int64_t blocks = ceil_div(n, 256);
+    int64_t cap = (int64_t)sm_count() * 16;
+    return (unsigned)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
+}
+
+int widen_i32_to_i64(const int32_t *src, int64_t *dst, int64_t n, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    widen_kernel<<<stream_grid(n), 256, 0, st>>>(src, dst, n);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// no alignment requirement (the vectorised narrow_i64_to_i32 wants 16-byte aligned input)
+int narrow_any_i64_to_i32(const int64_t *src, int32_t *dst, int64_t n, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    narrow_scalar_kernel<<<stream_grid(n), 256, 0, st>>>(src, dst, n);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
 int narrow_i64_to_i32(const int64_t *src, int32_t *dst, int64_t n, cudaStream_t st)
 {
     if (n <= 0) return 0;

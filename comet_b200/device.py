@@ -39,8 +39,9 @@ def to_device(A, device="cuda", pin=False):
             t = t.pin_memory()
         return t.to(device, non_blocking=pin)
 
-    row_ids = up(A.a1crd[:int(A.a1pos[1])]) if A.format == "DCSR" else None
-    return DeviceCSR(A.nrows, A.ncols, up(A.a2pos), up(A.a2crd), up(A.val), row_ids)
+    i64 = lambda a: np.asarray(a, dtype=np.int64)       # the device entry points take int64 indices
+    row_ids = up(i64(A.a1crd[:int(A.a1pos[1])])) if A.format == "DCSR" else None
+    return DeviceCSR(A.nrows, A.ncols, up(i64(A.a2pos)), up(i64(A.a2crd)), up(A.val), row_ids)
 
 
 def _p(t):

@@ -185,6 +185,41 @@ COMET_B200_EXPORT void comet_b200_masked_spgemm_count_f64_i64(
     int32_t semiring, int64_t out_rank, void *out_ptr);
 
 /* ------------------------------------------------------------------------- */
+/* The same entry points for 32-bit index arrays (pos / crd memrefs of i32;    */
+/* dims, sizes and the count stay 64-bit).  COMET picks the index width per    */
+/* tensor type: i64 on its CPU target (frontends/comet_dsl/comet.cpp:817-823), */
+/* and cometpy keeps scipy's int32 index arrays, which instantiates the _i32   */
+/* runtime symbols (frontends/numpy-scipy/cometpy/comet.py:198-218; compare    */
+/* read_input_2D_f64_i32, lib/ExecutionEngine/SparseUtils.cpp:2396).  Indices  */
+/* are widened on the device; a sparse result with 2^31-1 or more entries is   */
+/* refused.  A handle must be finished by the numeric call of the same width.  */
+/* ------------------------------------------------------------------------- */
+COMET_B200_EXPORT void comet_b200_spmv_f64_i32(COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr,
+                                               int64_t y_rank, void *y_ptr, int32_t semiring,
+                                               int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_spmm_f64_i32(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                                               int64_t C_rank, void *C_ptr, int32_t semiring,
+                                               int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_sddmm_f64_i32(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr,
+                                                int64_t D_rank, void *D_ptr,
+                                                COMET_B200_SPARSE2D(O));
+COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_f64_i32(COMET_B200_SPARSE2D(A),
+                                                                 int64_t B_rank, void *B_ptr,
+                                                                 COMET_B200_SPARSE2D(C));
+COMET_B200_EXPORT int64_t comet_b200_spgemm_symbolic_f64_i32(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr);
+COMET_B200_EXPORT void comet_b200_spgemm_numeric_f64_i32(int64_t handle, int64_t C2crd_rank,
+                                                         void *C2crd_ptr, int64_t Cval_rank,
+                                                         void *Cval_ptr);
+COMET_B200_EXPORT int64_t comet_b200_elews_mul_sparse_sparse_symbolic_f64_i32(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), int64_t C2pos_rank, void *C2pos_ptr,
+    int64_t sizes_rank, void *sizes_ptr);
+COMET_B200_EXPORT void comet_b200_masked_spgemm_count_f64_i32(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t out_rank, void *out_ptr);
+
+/* ------------------------------------------------------------------------- */
 /* Error reporting (COMET's runtime has none beyond stderr + exit; see         */
 /* SparseUtils.cpp:158-168).                                                   */
 /* ------------------------------------------------------------------------- */

@@ -230,3 +230,38 @@ def test_einsum_surface_matches_cometpy_forms():
     want.sort_indices(); want.eliminate_zeros()
     got = C.to_scipy(); got.eliminate_zeros()
     assert (abs(got - want)).nnz == 0
+
+
+def test_int32_index_entry_points_match_int64():
+    """scipy's default int32 index arrays go through the _f64_i32 symbols (indices widened on the
+    device) and give the same results, with int32 structure arrays coming back."""
+    A64 = datasets.rmat_csr(11, 8, seed=7)
+    A32 = A64.with_index_dtype(np.int32)
+    assert A32.index_dtype == np.int32
+    x = datasets.dense_uniform(A64.ncols, 1)
+    B = datasets.dense_uniform((A64.ncols, 16), 2)
+    assert np.array_equal(api.spmv(A32, x), api.spmv(A64, x))
+    np.testing.assert_allclose(api.spmm(A32, B), api.spmm(A64, B), rtol=1e-13, atol=1e-13)
+    X = datasets.dense_uniform((A64.nrows, 8), 3)
+    Y = datasets.dense_uniform((A64.ncols, 8), 4)
+    assert np.array_equal(api.sddmm(A32, X, Y), api.sddmm(A64, X, Y))
+    D = datasets.dense_uniform((A64.nrows, A64.ncols), 5)
+    assert np.array_equal(api.elews_sparse_dense(A32, D), api.elews_sparse_dense(A64, D))
+    C32, C64 = api.spgemm(A32, A32), api.spgemm(A64, A64)
+    assert C32.a2pos.dtype == np.int32 and C32.a2crd.dtype == np.int32
+    assert np.array_equal(C32.a2pos, C64.a2pos) and np.array_equal(C32.a2crd, C64.a2crd)
+    np.testing.assert_allclose(C32.val, C64.val, rtol=1e-13)
+    M32 = api.spgemm(A32, A32, A32, api.PLUS_PAIR)
+    ref = oracle.spgemm(_orc(A64), _orc(A64), _orc(A64), oracle.PLUS_PAIR)
+    assert np.array_equal(M32.a2pos, ref.a2pos) and np.array_equal(M32.a2crd, ref.a2crd)
+    E32 = api.elews_csr_csr(A32, A32)
+    assert E32.a2crd.dtype == np.int32 and np.array_equal(E32.a2crd, A64.a2crd)
+    L = datasets.config_triangles(scale=10, edge_factor=8)
+    assert api.triangle_count(L.with_index_dtype(np.int32)) == api.triangle_count(L)
+    # mixed widths are promoted to int64
+    assert api.spgemm(A32, A64).a2crd.dtype == np.int64
+    # COO and DCSR operands with int32 indices
+    import scipy.sparse as sp
+    coo = A64.to_scipy().tocoo()
+    assert coo.row.dtype == np.int32
+    np.testing.assert_allclose(api.spmv(coo, x), api.spmv(A64, x), rtol=1e-13, atol=1e-13)
