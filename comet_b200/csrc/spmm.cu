@@ -19,7 +19,7 @@
 namespace cb200 {
 
 static const int SPMM_THREADS = 256;
-static const int SPMM_PASSES = 2;
+static const int SPMM_FETCH = 8;            // rows per lane group per draw
 static const int64_t SPMM_LONG_ROW = 512;
 static const int64_t SPMM_CHUNK = 512;
 
@@ -69,19 +69,28 @@ spmm_rows_kernel(int64_t nrows, const int64_t *__restrict__ row_ids,
                  double *__restrict__ c, int64_t ldc, int k, int slice_cols, int64_t row_blocks,
                  int accumulate, int pair, WorkHeader *hdr, Chunk *chunks, unsigned chunk_cap)
 {
-    constexpr int GROUPS = SPMM_THREADS / T;
-    constexpr int ROWS = GROUPS * SPMM_PASSES;
-    const int g = threadIdx.x / T, l = threadIdx.x % T;
+    // Persistent warps draw blocks of rows from a counter (hdr->pad[0]): with rows of very
+    // different lengths a static assignment leaves most warps of a CTA idle while one finishes.
+    constexpr int GPW = 32 / T;                       // lane groups (rows in flight) per warp
+    constexpr int BLOCK_ROWS = GPW * SPMM_FETCH;      // rows per draw
+    const int l = threadIdx.x % T;
     const int lane = threadIdx.x & 31;
+    const int gw = lane / T;
     const unsigned gmask = (T == 32) ? 0xffffffffu : (((1u << T) - 1u) << (lane & ~(T - 1)));
-    const int slice = (int)(blockIdx.x / row_blocks);
-    const int64_t row0 = (int64_t)(blockIdx.x % row_blocks) * ROWS;
-    const int col0 = slice * slice_cols;
-    const int ncol2 = ((k - col0) < slice_cols ? (k - col0) : slice_cols) / 2;
-    const double *bpanel = b + col0;
-
-    for (int pass = 0; pass < SPMM_PASSES; pass++) {
-        int64_t r = row0 + pass * GROUPS + g;
+    const int64_t total_items = row_blocks * (int64_t)((k + slice_cols - 1) / slice_cols);
+    while (true) {
+        __syncwarp();
+        unsigned item = 0;
+        if (lane == 0) item = atomicAdd(&hdr->pad[0], 1u);
+        item = __shfl_sync(0xffffffffu, item, 0);
+        if ((int64_t)item >= total_items) break;
+        const int slice = (int)(item / row_blocks);
+        const int64_t row0 = (int64_t)(item % row_blocks) * BLOCK_ROWS;
+        const int col0 = slice * slice_cols;
+        const int ncol2 = ((k - col0) < slice_cols ? (k - col0) : slice_cols) / 2;
+        const double *bpanel = b + col0;
+    for (int pass = 0; pass < SPMM_FETCH; pass++) {
+        int64_t r = row0 + pass * GPW + gw;
         if (r >= nrows) break;
         int64_t s = pos[r], e = pos[r + 1];
         int64_t out = row_ids ? row_ids[r] : r;
@@ -122,6 +131,7 @@ spmm_rows_kernel(int64_t nrows, const int64_t *__restrict__ row_ids,
                 __stcs(crow + l + i * T, o);   // written once, never re-read: keep it out of B's way in L2
             }
         }
+    }
     }
 }
 
@@ -217,10 +227,13 @@ struct SpmmArgs {
 template <int T, int NI, typename IdxT>
 static int launch_panels(const SpmmArgs &a)
 {
-    constexpr int ROWS = (SPMM_THREADS / T) * SPMM_PASSES;
-    int64_t row_blocks = ceil_div(a.nrows, ROWS);
-    int64_t grid = row_blocks * a.nslices;
-    if (grid > 0x7fffffffLL) return fail("spmm: grid too large");
+    constexpr int BLOCK_ROWS = (32 / T) * SPMM_FETCH;
+    int64_t row_blocks = ceil_div(a.nrows, BLOCK_ROWS);
+    int64_t items = row_blocks * a.nslices;
+    if (items > 0xfffffff0LL) return fail("spmm: too many row blocks");
+    int64_t grid = ceil_div(items, SPMM_THREADS / 32);
+    const int64_t persistent = (int64_t)sm_count() * 8;
+    if (grid > persistent) grid = persistent;
     spmm_rows_kernel<T, NI, IdxT><<<(unsigned)grid, SPMM_THREADS, 0, a.st>>>(
         a.nrows, a.row_ids, a.pos, (const IdxT *)a.crd, a.val, a.b, a.ldb, a.c, a.ldc, a.k,
         a.slice_cols, row_blocks, a.accumulate, a.pair, a.hdr, a.chunks, a.chunk_cap);
