@@ -60,3 +60,21 @@ def test_bad_descriptors_are_rejected_on_the_host():
         comet_b200.spmv(ok, np.ones(1))
     with pytest.raises(ValueError, match="semiring"):
         comet_b200.spmv(ok, np.ones(2), semiring="min,plus")
+
+
+def test_default_error_mode_exits_like_the_reference_runtime():
+    """Without COMET_B200_ON_ERROR=return a failure prints a message and exits with status 1, which is
+    what COMET's own runtime does (lib/ExecutionEngine/SparseUtils.cpp:158-168)."""
+    import subprocess
+    import sys
+    code = (
+        "import ctypes, sys; sys.path.insert(0, %r)\n"
+        "from comet_b200 import _lib\n"
+        "lib = ctypes.CDLL(_lib.LIB_PATH)\n"
+        "lib.comet_b200_spgemm_numeric_f64_i64.argtypes = [ctypes.c_int64] + [ctypes.c_int64, ctypes.c_void_p] * 2\n"
+        "lib.comet_b200_spgemm_numeric_f64_i64(12345, 1, None, 1, None)\n"
+        "print('survived')\n" % ROOT)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 1
+    assert "libcomet_b200: ERROR" in r.stderr and "unknown handle" in r.stderr
+    assert "survived" not in r.stdout

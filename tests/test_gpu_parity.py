@@ -265,3 +265,57 @@ def test_int32_index_entry_points_match_int64():
     coo = A64.to_scipy().tocoo()
     assert coo.row.dtype == np.int32
     np.testing.assert_allclose(api.spmv(coo, x), api.spmv(A64, x), rtol=1e-13, atol=1e-13)
+
+
+def test_empty_and_degenerate_inputs():
+    """Zero rows, zero stored entries, all-empty rows, a single entry: nothing is launched out of
+    bounds and outputs follow the accumulate semantics."""
+    import scipy.sparse as sp
+    Z = api.as_sparse(sp.csr_matrix((50, 40)))                     # no stored entries
+    x = np.ones(40)
+    assert np.array_equal(api.spmv(Z, x), np.zeros(50))
+    y0 = np.arange(50, dtype=np.float64)
+    assert np.array_equal(api.spmv(Z, x, y0), y0)                  # accumulate keeps the old values
+    assert np.array_equal(api.spmm(Z, np.ones((40, 6))), np.zeros((50, 6)))
+    assert api.sddmm(Z, np.ones((50, 4)), np.ones((40, 4))).shape == (0,)
+    assert api.spgemm(Z, api.as_sparse(sp.csr_matrix((40, 30)))).nnz == 0
+    assert api.masked_pair_count(Z, api.as_sparse(sp.csr_matrix((40, 40))), Z) == 0
+    E = api.as_sparse(sp.csr_matrix((0, 7)))                       # no rows at all
+    assert api.spmv(E, np.ones(7)).shape == (0,)
+    one = api.as_sparse(sp.csr_matrix(([2.5], ([3], [1])), shape=(5, 4)))
+    assert np.array_equal(api.spmv(one, np.array([1.0, 2.0, 3.0, 4.0])), [0, 0, 0, 5.0, 0])
+    C = api.spgemm(one, api.as_sparse(sp.csr_matrix(([4.0], ([1], [2])), shape=(4, 6))))
+    assert C.nnz == 1 and C.a2crd[0] == 2 and C.val[0] == 10.0 and list(C.a2pos) == [0, 0, 0, 0, 1, 1]
+
+
+def test_handles_are_single_use_and_checked():
+    from comet_b200._lib import CometB200Error
+    A = datasets.rmat_csr(8, 4, seed=2)
+    dA = dev.to_device(A)
+    h, cpos, nnz = dev.spgemm_symbolic(dA, dA)
+    dev.spgemm_numeric(h, nnz, "cuda")
+    with pytest.raises(CometB200Error, match="unknown handle"):
+        dev.spgemm_numeric(h, nnz, "cuda")                          # released by the first numeric call
+    h2, _, _ = dev.spgemm_symbolic(dA, dA)
+    from comet_b200 import _lib
+    _lib.load().comet_b200_handle_destroy(h2)                       # dropping without numeric is allowed
+    with pytest.raises(CometB200Error, match="unknown handle"):
+        dev.spgemm_numeric(h2, nnz, "cuda")
+
+
+def test_unaligned_device_arrays_take_the_scalar_paths():
+    """Views that start 8 bytes into an allocation break the 16-byte alignment the vector loads want;
+    SpMV and SpMM fall back to scalar loads, operations that cannot say so."""
+    from comet_b200._lib import CometB200Error
+    A = datasets.rmat_csr(9, 8, seed=4)
+    x = datasets.dense_uniform(A.ncols, 1)
+    pad = lambda a: torch.from_numpy(np.concatenate([np.zeros(1, dtype=a.dtype), a])).cuda()[1:]
+    dA = dev.DeviceCSR(A.nrows, A.ncols, torch.from_numpy(A.a2pos).cuda(), pad(A.a2crd), pad(A.val))
+    assert dA.crd.data_ptr() % 16 == 8
+    want = oracle.spmv(_orc(A), x)
+    np.testing.assert_allclose(dev.spmv(dA, torch.from_numpy(x).cuda()).cpu().numpy(), want, rtol=1e-12, atol=1e-13)
+    B = datasets.dense_uniform((A.ncols, 8), 2)
+    np.testing.assert_allclose(dev.spmm(dA, torch.from_numpy(B).cuda()).cpu().numpy(), oracle.spmm(_orc(A), B),
+                               rtol=1e-12, atol=1e-13)
+    with pytest.raises(CometB200Error, match="aligned"):
+        dev.spgemm_symbolic(dA, dA)
