@@ -122,6 +122,18 @@ static int get_sparse(const char *what, int isz, int32_t f1, int32_t f2, int64_t
     }
     if (s->nnz < 0) return fail("%s: negative nnz", what);
     if (a2crd.n < s->nnz || val.n < s->nnz) return fail("%s: crd/val arrays shorter than nnz", what);
+    // The kernels trust the row pointer: check on the host that it starts at 0 and never decreases
+    // (one pass over rows+1 integers), so that a malformed descriptor -- e.g. 32-bit arrays handed to
+    // the 64-bit entry point -- is refused here instead of sending a kernel out of bounds.
+    if (s->fmt != F_COO && s->nstored > 0) {
+        int64_t prev = idx_get(s->a2pos, 0, isz);
+        if (prev != 0) return fail("%s: pos[0] must be 0 (got %lld)", what, (long long)prev);
+        for (int64_t i = 1; i <= s->nstored; i++) {
+            const int64_t cur = idx_get(s->a2pos, i, isz);
+            if (cur < prev) return fail("%s: pos decreases at row %lld (wrong index width?)", what, (long long)(i - 1));
+            prev = cur;
+        }
+    }
     return 0;
 }
 
@@ -271,6 +283,58 @@ static int spmv_host(const HostSparse &A, Arr x, Arr y, int semiring, int accumu
     return finish(st);
 }
 
+// Large SpMM through the host entry point is bound by PCIe: B goes up, C comes back.  The two
+// directions can run at the same time if the work is cut into column panels: panel j of B is
+// uploaded while panel j-1 is multiplied and panel j-2 of C is downloaded (strided 2-D copies
+// between the row-major host matrices and packed panels on the device, two buffers each).
+static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &bag, const Mat &B, const Mat &C,
+                            int semiring, int64_t panel, cudaStream_t st)
+{
+    cudaStream_t up = aux_stream(0), down = aux_stream(1);
+    if (!up || !down) return fail("spmm: could not create the copy streams");
+    const int64_t k = B.cols;
+    double *dB[2], *dC[2];
+    cudaEvent_t in[2], comp[2], out[2];
+    for (int i = 0; i < 2; i++) {
+        CB_TRY(bag.alloc((void **)&dB[i], (size_t)A.ncols * panel * 8));
+        CB_TRY(bag.alloc((void **)&dC[i], (size_t)A.nrows * panel * 8));
+        CB_CUDA(cudaEventCreateWithFlags(&in[i], cudaEventDisableTiming));
+        CB_CUDA(cudaEventCreateWithFlags(&comp[i], cudaEventDisableTiming));
+        CB_CUDA(cudaEventCreateWithFlags(&out[i], cudaEventDisableTiming));
+    }
+    cudaEvent_t ready;
+    CB_CUDA(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
+    CB_CUDA(cudaEventRecord(ready, st));                 // A is uploaded, panel buffers exist
+    CB_CUDA(cudaStreamWaitEvent(up, ready, 0));
+    CB_CUDA(cudaStreamWaitEvent(down, ready, 0));
+    int rc = 0;
+    int64_t j = 0;
+    for (int64_t c0 = 0; c0 < k && !rc; c0 += panel, j++) {
+        const int b = (int)(j & 1);
+        const int64_t w = (k - c0) < panel ? (k - c0) : panel;
+        if (j >= 2) CB_CUDA(cudaStreamWaitEvent(up, comp[b], 0));       // panel j-2 no longer reads dB[b]
+        CB_CUDA(cudaMemcpy2DAsync(dB[b], (size_t)panel * 8, B.data + c0, (size_t)B.s0 * 8, (size_t)w * 8,
+                                  (size_t)A.ncols, cudaMemcpyHostToDevice, up));
+        CB_CUDA(cudaEventRecord(in[b], up));
+        CB_CUDA(cudaStreamWaitEvent(st, in[b], 0));
+        if (j >= 2) CB_CUDA(cudaStreamWaitEvent(st, out[b], 0));        // panel j-2 has left dC[b]
+        rc = comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, w, dA.row_ids, dA.pos, dA.crd, dA.val, dB[b],
+                                         panel, dC[b], panel, semiring, 0, 0, st);
+        if (rc) break;
+        CB_CUDA(cudaEventRecord(comp[b], st));
+        CB_CUDA(cudaStreamWaitEvent(down, comp[b], 0));
+        CB_CUDA(cudaMemcpy2DAsync(C.data + c0, (size_t)C.s0 * 8, dC[b], (size_t)panel * 8, (size_t)w * 8,
+                                  (size_t)A.nrows, cudaMemcpyDeviceToHost, down));
+        CB_CUDA(cudaEventRecord(out[b], down));
+    }
+    cudaError_t e1 = cudaStreamSynchronize(up), e2 = cudaStreamSynchronize(down), e3 = cudaStreamSynchronize(st);
+    for (int i = 0; i < 2; i++) { cudaEventDestroy(in[i]); cudaEventDestroy(comp[i]); cudaEventDestroy(out[i]); }
+    cudaEventDestroy(ready);
+    if (rc) return rc;
+    if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) return fail("spmm: panel pipeline failed");
+    return 0;
+}
+
 static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiring, int accumulate)
 {
     if (B.rows < A.ncols) return fail("spmm: B has fewer rows than A has columns");
@@ -283,6 +347,19 @@ static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiri
     DevSparse dA;
     CB_TRY(upload_sparse("spmm", A, bag, &dA));
     const int64_t k = B.cols;
+    {
+        // panels of 32 columns (256-byte rows) once the dense operands are big enough to matter
+        int64_t panel = 32;
+        const char *env = getenv("COMET_B200_SPMM_PANEL");
+        if (env) panel = atoll(env);
+        double min_bytes = 256e6;
+        const char *menv = getenv("COMET_B200_SPMM_PANEL_MIN_BYTES");
+        if (menv) min_bytes = atof(menv);
+        const bool big = (double)(A.ncols + A.nrows) * (double)k * 8.0 >= min_bytes;
+        if (!accumulate && A.fmt != F_DCSR && panel >= 2 && panel % 2 == 0 && k >= 2 * panel && big &&
+            semiring == COMET_B200_PLUS_TIMES)
+            return spmm_host_panels(A, dA, bag, B, C, semiring, panel, st);
+    }
     double *dB, *dC;
     CB_TRY(bag.upload((void **)&dB, B.data, (size_t)((A.ncols - 1) * B.s0 + k) * 8 * (A.ncols > 0)));
     size_t cbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * C.s0 + k) * 8 : 0;

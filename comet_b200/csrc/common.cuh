@@ -59,6 +59,7 @@ void scratch_release_all();
 
 int sm_count();
 cudaStream_t lib_stream();   // the library's own stream for the host-memref entry points
+cudaStream_t aux_stream(int i);   // two more streams (i = 0, 1) for copies that overlap with compute
 
 // ---------------------------------------------------------------------------
 // Small shared kernels (util.cu)

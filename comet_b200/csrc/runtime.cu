@@ -40,6 +40,7 @@ struct DeviceState {
     void *ptr[SLOT_COUNT];
     size_t cap[SLOT_COUNT];
     cudaStream_t stream;
+    cudaStream_t aux[2];
     int sms;
 };
 static DeviceState g_dev[kMaxDevices];
@@ -114,6 +115,17 @@ cudaStream_t lib_stream()
             s->stream = nullptr;
     }
     return s->stream;
+}
+
+cudaStream_t aux_stream(int i)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState *s = state();
+    if (!s || i < 0 || i > 1) return nullptr;
+    if (!s->aux[i]) {
+        if (cudaStreamCreateWithFlags(&s->aux[i], cudaStreamNonBlocking) != cudaSuccess) s->aux[i] = nullptr;
+    }
+    return s->aux[i];
 }
 
 }  // namespace cb200

@@ -60,6 +60,18 @@ def test_bad_descriptors_are_rejected_on_the_host():
         comet_b200.spmv(ok, np.ones(1))
     with pytest.raises(ValueError, match="semiring"):
         comet_b200.spmv(ok, np.ones(2), semiring="min,plus")
+    # 32-bit index arrays handed to the 64-bit entry point are refused on the host: read as
+    # int64 the row pointer no longer starts at 0 / stops being monotone
+    from comet_b200 import _lib
+    from comet_b200.api import _Packer
+    narrow = SparseTensor("CSR", 4, 4, np.array([4], dtype=np.int32), np.array([-1], dtype=np.int32),
+                          np.array([0, 1, 2, 3, 4, 0, 0, 0, 0, 0], dtype=np.int32),
+                          np.array([0, 1, 2, 3, 0, 0, 0, 0], dtype=np.int32), np.ones(8))
+    pk = _Packer()
+    x, y = np.ones(4), np.zeros(4)
+    _lib.load().comet_b200_spmv_f64_i64(*pk.sparse(narrow), *pk.m1(x), *pk.m1(y), 0, 0)
+    with pytest.raises(CometB200Error, match="pos"):
+        _lib.check()
 
 
 def test_default_error_mode_exits_like_the_reference_runtime():

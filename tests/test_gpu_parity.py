@@ -319,3 +319,37 @@ def test_unaligned_device_arrays_take_the_scalar_paths():
                                rtol=1e-12, atol=1e-13)
     with pytest.raises(CometB200Error, match="aligned"):
         dev.spgemm_symbolic(dA, dA)
+
+
+def test_spmm_host_entry_point_panel_pipeline(monkeypatch):
+    """Large SpMM calls through the host entry point are cut into column panels so that the upload of
+    B, the multiplication and the download of C overlap; force that path on a small input, with a
+    dense width that is not a multiple of the panel."""
+    A = _skewed(1200, seed=11)
+    for k, panel in ((10, 4), (64, 32), (6, 2)):
+        B = datasets.dense_uniform((A.ncols, k), k)
+        ref = oracle.spmm(_orc(A), B)
+        scale = oracle.spmm(_abs(A), np.abs(B))
+        monkeypatch.setenv("COMET_B200_SPMM_PANEL", str(panel))
+        monkeypatch.setenv("COMET_B200_SPMM_PANEL_MIN_BYTES", "0")
+        got = api.spmm(A, B)
+        monkeypatch.delenv("COMET_B200_SPMM_PANEL")
+        monkeypatch.delenv("COMET_B200_SPMM_PANEL_MIN_BYTES")
+        _close(got, ref, scale)
+        # strided (non-contiguous) host operands: a column window of wider matrices
+        wide = datasets.dense_uniform((A.ncols, k + 6), 99)
+        monkeypatch.setenv("COMET_B200_SPMM_PANEL", str(panel))
+        monkeypatch.setenv("COMET_B200_SPMM_PANEL_MIN_BYTES", "0")
+        lib_b = wide[:, 3:3 + k]
+        pk = api._Packer()
+        out = np.full((A.nrows, k + 4), -7.0)
+        from comet_b200 import _lib
+        lib = _lib.load()
+        fn, _, (A_,) = api._entry(lib, "spmm", api.as_sparse(A))      # entry point of A's index width
+        fn(*pk.sparse(A_), *pk.m2(lib_b), *pk.m2(out[:, 2:2 + k]), 0, 0)
+        _lib.check()
+        monkeypatch.delenv("COMET_B200_SPMM_PANEL")
+        monkeypatch.delenv("COMET_B200_SPMM_PANEL_MIN_BYTES")
+        _close(out[:, 2:2 + k], oracle.spmm(_orc(A), np.ascontiguousarray(lib_b)),
+               oracle.spmm(_abs(A), np.abs(np.ascontiguousarray(lib_b))))
+        assert np.all(out[:, :2] == -7.0) and np.all(out[:, 2 + k:] == -7.0)      # padding untouched
