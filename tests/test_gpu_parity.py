@@ -353,3 +353,15 @@ def test_spmm_host_entry_point_panel_pipeline(monkeypatch):
         _close(out[:, 2:2 + k], oracle.spmm(_orc(A), np.ascontiguousarray(lib_b)),
                oracle.spmm(_abs(A), np.abs(np.ascontiguousarray(lib_b))))
         assert np.all(out[:, :2] == -7.0) and np.all(out[:, 2 + k:] == -7.0)      # padding untouched
+
+
+def test_spmv_large_power_law_uses_the_chunk_list():
+    """Above 2^20 stored entries long rows are cut into chunks handled by a second launch."""
+    A = datasets.rmat_csr(17, 16, seed=3)
+    assert A.nnz > (1 << 20) and np.diff(A.a2pos).max() > 2048
+    x = datasets.dense_uniform(A.ncols, 1)
+    y0 = datasets.dense_uniform(A.nrows, 2)
+    scale = oracle.spmv(_abs(A), np.abs(x), np.abs(y0))
+    _close(api.spmv(A, x), oracle.spmv(_orc(A), x), scale)
+    _close(api.spmv(A, x, y0), oracle.spmv(_orc(A), x, y0), scale)
+    assert np.array_equal(api.spmv(A, x, semiring=api.PLUS_PAIR), np.diff(A.a2pos).astype(np.float64))
