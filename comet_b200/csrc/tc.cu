@@ -6,19 +6,24 @@
 //
 // Same structure as the reference's push mask (set the bits of M's row i, test
 // every product's column, clear them).  The bit array over all columns does not
-// fit shared memory, so the mask row is held there as a one-hash Bloom filter
-// (one bit test, no loop, rejects almost every miss) backed by an open-addressing
-// hash set that confirms the few positives.  Rows are binned by the length of
-// their mask row:
+// fit shared memory, so the mask row is held there as a cuckoo hash set: two
+// tables, two hash functions, every coordinate sits in one of its two slots.  A
+// probe is therefore two 32-bit shared-memory loads and two compares -- the same
+// short instruction sequence for a hit and for a miss, with no loop, so the
+// lanes of a warp do not diverge (about one probe in fourteen is a hit, so a
+// filter in front of a looping table sent almost every warp down the slow path).
+// The set is built at a load factor of 1/4; if an insertion chain does not end
+// within its bound the row falls back to linear probing in the same memory.
+// Rows are binned by the length of their mask row:
 //   <= 128 entries   one warp per row
 //   <= 2048 entries  one CTA per row
-//   longer           cut into units of (8192 mask entries) x (2048 entries of A),
+//   longer           cut into units of (4096 mask entries) x (2048 entries of A),
 //                    one CTA per unit, so a huge row spreads over many SMs
 // and rows / units are handed out dynamically (one atomic each), because the work
 // per row (sum of the lengths of the B rows it touches) is very uneven.
-// Every element of every touched B row is read (coalesced, int32) and tested
-// once per mask segment, so the number of probes equals the reference's.
-// Coordinates are narrowed to int32 once per call (scratch memory).
+// Every element of every touched B row is read (coalesced, 128-bit loads of int32
+// coordinates) and tested once per mask segment, so the number of probes equals
+// the reference's.  Coordinates are narrowed to int32 once per call (scratch memory).
 //
 // Counts are exact int64; no floating point is involved.
 #include "common.cuh"
@@ -26,16 +31,14 @@
 namespace cb200 {
 
 static const int TC_WARP_MAX = 128;      // mask-row length handled by a warp
-static const int TC_WARP_TAB = 8;        // log2 slots of its hash set
-static const int TC_WARP_BLOOM = 12;     // log2 bits of its Bloom filter
+static const int TC_WARP_LOG2 = 9;       // log2 slots of its set (both tables together)
 static const int TC_WARPS = 8;           // warps per CTA in the warp kernel
 static const int TC_MID_MAX = 2048;
-static const int TC_MID_TAB = 12;
-static const int TC_MID_BLOOM = 15;
-static const int TC_BIG_SEG = 8192;      // mask entries per unit
+static const int TC_MID_LOG2 = 13;
+static const int TC_BIG_SEG = 4096;      // mask entries per unit
 static const int TC_BIG_SLICE = 2048;    // entries of A per unit
-static const int TC_BIG_TAB = 14;
-static const int TC_BIG_BLOOM = 17;
+static const int TC_BIG_LOG2 = 14;
+static const int TC_CUCKOO_CHAIN = 48;   // longest eviction chain before the row falls back
 
 struct TcUnit {
     int32_t row;
@@ -48,6 +51,35 @@ struct TcHeader {
     unsigned next[4];    // next item to hand out per list
 };
 
+// --- cuckoo set: tables T0 = tab[0, H) and T1 = tab[H, 2H), H = 2^(LOG2-1) -------------------------
+template <int LOG2>
+__device__ __forceinline__ unsigned tc_h0(int32_t j)
+{
+    return ((uint32_t)j * 0x9E3779B1u) >> (33 - LOG2);
+}
+
+template <int LOG2>
+__device__ __forceinline__ unsigned tc_h1(int32_t j)
+{
+    return (1u << (LOG2 - 1)) + (((uint32_t)j * 0x85EBCA6Bu + 0x6D2B79F5u) >> (33 - LOG2));
+}
+
+// Returns false if the eviction chain did not end.
+template <int LOG2>
+__device__ __forceinline__ bool tc_cuckoo_insert(int32_t *tab, int32_t key)
+{
+    bool second = false;
+    for (int it = 0; it < TC_CUCKOO_CHAIN; it++) {
+        const unsigned pos = second ? tc_h1<LOG2>(key) : tc_h0<LOG2>(key);
+        const int32_t old = atomicExch(&tab[pos], key);
+        if (old == -1 || old == key) return true;
+        key = old;                 // the evicted coordinate moves to its slot in the other table
+        second = !second;
+    }
+    return false;
+}
+
+// --- fallback: linear probing over all 2^LOG2 slots -------------------------------------------
 template <int LOG2>
 __device__ __forceinline__ unsigned tc_slot(int32_t j)
 {
@@ -55,7 +87,7 @@ __device__ __forceinline__ unsigned tc_slot(int32_t j)
 }
 
 template <int LOG2>
-__device__ __forceinline__ void tc_insert(int32_t *tab, int32_t j)
+__device__ __forceinline__ void tc_linear_insert(int32_t *tab, int32_t j)
 {
     unsigned h = tc_slot<LOG2>(j);
     for (int probe = 0; probe < (1 << LOG2); probe++) {
@@ -66,7 +98,7 @@ __device__ __forceinline__ void tc_insert(int32_t *tab, int32_t j)
 }
 
 template <int LOG2>
-__device__ __forceinline__ unsigned tc_confirm(const int32_t *tab, int32_t j)
+__device__ __forceinline__ unsigned tc_linear_probe(const int32_t *tab, int32_t j)
 {
     unsigned h = tc_slot<LOG2>(j);
     for (int probe = 0; probe < (1 << LOG2); probe++) {
@@ -78,40 +110,41 @@ __device__ __forceinline__ unsigned tc_confirm(const int32_t *tab, int32_t j)
     return 0u;
 }
 
-// Bloom filter with a single hash: bit = top BLOOM bits of the multiplicative hash.
-template <int BLOOM>
-__device__ __forceinline__ unsigned tc_bit(int32_t j)
+// `linear` is uniform over the threads that share the set.
+template <int LOG2>
+__device__ __forceinline__ unsigned tc_probe(const int32_t *tab, bool linear, int32_t j)
 {
-    return ((uint32_t)j * 0x85EBCA6Bu) >> (32 - BLOOM);
+    if (linear) return tc_linear_probe<LOG2>(tab, j);
+    return (unsigned)(tab[tc_h0<LOG2>(j)] == j) | (unsigned)(tab[tc_h1<LOG2>(j)] == j);
 }
 
-template <int LOG2, int BLOOM>
-__device__ __forceinline__ unsigned tc_probe(const int32_t *tab, const uint32_t *bloom, int32_t j)
-{
-    const unsigned b = tc_bit<BLOOM>(j);
-    if (!((bloom[b >> 5] >> (b & 31)) & 1u)) return 0u;
-    return tc_confirm<LOG2>(tab, j);
-}
-
-// Clears and fills filter and set with mask entries [ms, me); `nthreads` threads with index `tid` cooperate.
-template <int LOG2, int BLOOM>
-__device__ __forceinline__ void tc_fill(int32_t *tab, uint32_t *bloom, const int32_t *__restrict__ mcrd,
+// Clears and fills the set with mask entries [ms, me); `nthreads` threads with index `tid` cooperate
+// (a warp when !block, the whole CTA otherwise; `flag` is a shared-memory word they all see).
+// Returns true if the set had to fall back to linear probing.
+template <int LOG2>
+__device__ __forceinline__ bool tc_fill(int32_t *tab, unsigned *flag, const int32_t *__restrict__ mcrd,
                                         int64_t ms, int64_t me, int tid, int nthreads, bool block)
 {
     for (int s = tid; s < (1 << LOG2); s += nthreads) tab[s] = -1;
-    for (int s = tid; s < (1 << (BLOOM - 5)); s += nthreads) bloom[s] = 0u;
+    if (tid == 0) *flag = 0u;
     if (block) __syncthreads(); else __syncwarp();
-    for (int64_t t = ms + tid; t < me; t += nthreads) {
-        const int32_t j = mcrd[t];
-        tc_insert<LOG2>(tab, j);
-        const unsigned b = tc_bit<BLOOM>(j);
-        atomicOr(&bloom[b >> 5], 1u << (b & 31));
+    bool ok = true;
+    for (int64_t t = ms + tid; t < me; t += nthreads) ok = tc_cuckoo_insert<LOG2>(tab, mcrd[t]) && ok;
+    if (!ok) *flag = 1u;
+    if (block) __syncthreads(); else __syncwarp();
+    const bool linear = *flag != 0u;
+    if (linear) {
+        if (block) __syncthreads(); else __syncwarp();
+        for (int s = tid; s < (1 << LOG2); s += nthreads) tab[s] = -1;
+        if (block) __syncthreads(); else __syncwarp();
+        for (int64_t t = ms + tid; t < me; t += nthreads) tc_linear_insert<LOG2>(tab, mcrd[t]);
+        if (block) __syncthreads(); else __syncwarp();
     }
-    if (block) __syncthreads(); else __syncwarp();
+    return linear;
 }
 
 // Streams the B rows named by entries [as, ae) of A's row and counts the elements
-// found in the filter + set.  Entries are taken in batches of 32: with `next`
+// found in the set.  Entries are taken in batches of 32: with `next`
 // null the calling warp walks all batches itself; otherwise the warps of a CTA
 // draw batch numbers from the shared counter `*next`, so a warp that meets short
 // B rows simply draws more batches.  A batch's B-row bounds are fetched by the 32
@@ -120,8 +153,8 @@ __device__ __forceinline__ void tc_fill(int32_t *tab, uint32_t *bloom, const int
 // 128-bit loads (four coordinates per lane, two loads in flight); a B row is
 // entered at the 16-byte boundary below its first element and the elements
 // outside [bs, be) are masked off.
-template <int LOG2, int BLOOM>
-__device__ __forceinline__ unsigned long long tc_stream_rows(const int32_t *tab, const uint32_t *bloom,
+template <int LOG2>
+__device__ __forceinline__ unsigned long long tc_stream_rows(const int32_t *tab, bool linear,
                                                             int64_t as, int64_t ae, unsigned *next,
                                                             int lane, const int32_t *__restrict__ acrd,
                                                             const int64_t *__restrict__ bpos,
@@ -155,23 +188,23 @@ __device__ __forceinline__ unsigned long long tc_stream_rows(const int32_t *tab,
                 const bool two = q + 128 < be;
                 if (two) v1 = __ldg((const int4 *)(bcrd + q + 128));
                 if (q >= bs && q + 3 < be) {
-                    h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.x) + tc_probe<LOG2, BLOOM>(tab, bloom, v0.y) +
-                           tc_probe<LOG2, BLOOM>(tab, bloom, v0.z) + tc_probe<LOG2, BLOOM>(tab, bloom, v0.w);
+                    h32 += tc_probe<LOG2>(tab, linear, v0.x) + tc_probe<LOG2>(tab, linear, v0.y) +
+                           tc_probe<LOG2>(tab, linear, v0.z) + tc_probe<LOG2>(tab, linear, v0.w);
                 } else {
-                    if (q >= bs) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.x);
-                    if (q + 1 >= bs && q + 1 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.y);
-                    if (q + 2 >= bs && q + 2 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.z);
-                    if (q + 3 >= bs && q + 3 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v0.w);
+                    if (q >= bs) h32 += tc_probe<LOG2>(tab, linear, v0.x);
+                    if (q + 1 >= bs && q + 1 < be) h32 += tc_probe<LOG2>(tab, linear, v0.y);
+                    if (q + 2 >= bs && q + 2 < be) h32 += tc_probe<LOG2>(tab, linear, v0.z);
+                    if (q + 3 >= bs && q + 3 < be) h32 += tc_probe<LOG2>(tab, linear, v0.w);
                 }
                 if (two) {
                     const int64_t r = q + 128;           // r >= bs always: it lies past the first vector
                     if (r + 3 < be) {
-                        h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.x) + tc_probe<LOG2, BLOOM>(tab, bloom, v1.y) +
-                               tc_probe<LOG2, BLOOM>(tab, bloom, v1.z) + tc_probe<LOG2, BLOOM>(tab, bloom, v1.w);
+                        h32 += tc_probe<LOG2>(tab, linear, v1.x) + tc_probe<LOG2>(tab, linear, v1.y) +
+                               tc_probe<LOG2>(tab, linear, v1.z) + tc_probe<LOG2>(tab, linear, v1.w);
                     } else {
-                        h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.x);
-                        if (r + 1 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.y);
-                        if (r + 2 < be) h32 += tc_probe<LOG2, BLOOM>(tab, bloom, v1.z);
+                        h32 += tc_probe<LOG2>(tab, linear, v1.x);
+                        if (r + 1 < be) h32 += tc_probe<LOG2>(tab, linear, v1.y);
+                        if (r + 2 < be) h32 += tc_probe<LOG2>(tab, linear, v1.z);
                     }
                 }
             }
@@ -239,8 +272,8 @@ tc_warp_kernel(TcHeader *hdr, const int32_t *__restrict__ list, const int64_t *_
                const int32_t *__restrict__ bcrd, const int64_t *__restrict__ mpos,
                const int32_t *__restrict__ mcrd, unsigned long long *__restrict__ count)
 {
-    __shared__ int32_t s_tab[TC_WARPS][1 << TC_WARP_TAB];
-    __shared__ uint32_t s_bloom[TC_WARPS][1 << (TC_WARP_BLOOM - 5)];
+    __shared__ int32_t s_tab[TC_WARPS][1 << TC_WARP_LOG2];
+    __shared__ unsigned s_flag[TC_WARPS];
     __shared__ unsigned long long s_part[TC_WARPS];
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned nlist = hdr->count[0];
@@ -251,8 +284,8 @@ tc_warp_kernel(TcHeader *hdr, const int32_t *__restrict__ list, const int64_t *_
         idx = __shfl_sync(0xffffffffu, idx, 0);
         if (idx >= nlist) break;
         const int64_t i = list[idx];
-        tc_fill<TC_WARP_TAB, TC_WARP_BLOOM>(s_tab[w], s_bloom[w], mcrd, mpos[i], mpos[i + 1], lane, 32, false);
-        hits += tc_stream_rows<TC_WARP_TAB, TC_WARP_BLOOM>(s_tab[w], s_bloom[w], apos[i], apos[i + 1], nullptr,
+        const bool linear = tc_fill<TC_WARP_LOG2>(s_tab[w], &s_flag[w], mcrd, mpos[i], mpos[i + 1], lane, 32, false);
+        hits += tc_stream_rows<TC_WARP_LOG2>(s_tab[w], linear, apos[i], apos[i + 1], nullptr,
                                                            lane, acrd, bpos, bcrd);
         __syncwarp();
     }
@@ -269,7 +302,7 @@ tc_warp_kernel(TcHeader *hdr, const int32_t *__restrict__ list, const int64_t *_
 
 // MODE 0: list of rows, whole row per CTA (mask taken in segments of SEG entries).
 // MODE 1: list of units (mask segment x slice of A's entries).
-template <int THREADS, int LOG2, int BLOOM, int SEG, int MODE>
+template <int THREADS, int LOG2, int SEG, int MODE>
 __global__ void __launch_bounds__(THREADS)
 tc_block_kernel(TcHeader *hdr, int which, const int32_t *__restrict__ list,
                 const TcUnit *__restrict__ units, const int64_t *__restrict__ apos,
@@ -282,7 +315,7 @@ tc_block_kernel(TcHeader *hdr, int which, const int32_t *__restrict__ list,
     __shared__ unsigned long long s_part[THREADS / 32];
     __shared__ unsigned s_idx, s_batch;
     int32_t *tab = s_dyn_tc;
-    uint32_t *bloom = (uint32_t *)(s_dyn_tc + (1 << LOG2));
+    __shared__ unsigned s_flag;
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned nlist = hdr->count[which];
     if (MODE == 1 && nlist > unit_cap) nlist = unit_cap;
@@ -309,8 +342,8 @@ tc_block_kernel(TcHeader *hdr, int which, const int32_t *__restrict__ list,
         for (int64_t seg = ms; seg < me; seg += SEG) {
             const int64_t seg_end = seg + SEG < me ? seg + SEG : me;
             if (threadIdx.x == 0) s_batch = 0;
-            tc_fill<LOG2, BLOOM>(tab, bloom, mcrd, seg, seg_end, threadIdx.x, THREADS, true);
-            hits += tc_stream_rows<LOG2, BLOOM>(tab, bloom, as, ae, &s_batch, lane, acrd, bpos, bcrd);
+            const bool linear = tc_fill<LOG2>(tab, &s_flag, mcrd, seg, seg_end, threadIdx.x, THREADS, true);
+            hits += tc_stream_rows<LOG2>(tab, linear, as, ae, &s_batch, lane, acrd, bpos, bcrd);
             __syncthreads();
         }
     }
@@ -367,20 +400,20 @@ int masked_pair_count(int64_t row_lo, int64_t row_hi, int64_t ncols, int64_t nnz
     const unsigned sms = (unsigned)sm_count();
     {   // longest rows first
         constexpr int T = 512;
-        const size_t smem = (sizeof(int32_t) << TC_BIG_TAB) + (sizeof(uint32_t) << (TC_BIG_BLOOM - 5));
-        auto kunits = tc_block_kernel<T, TC_BIG_TAB, TC_BIG_BLOOM, TC_BIG_SEG, 1>;
-        auto kslow = tc_block_kernel<T, TC_BIG_TAB, TC_BIG_BLOOM, TC_BIG_SEG, 0>;
+        const size_t smem = sizeof(int32_t) << TC_BIG_LOG2;
+        auto kunits = tc_block_kernel<T, TC_BIG_LOG2, TC_BIG_SEG, 1>;
+        auto kslow = tc_block_kernel<T, TC_BIG_LOG2, TC_BIG_SEG, 0>;
         CB_CUDA(cudaFuncSetAttribute(kunits, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         CB_CUDA(cudaFuncSetAttribute(kslow, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kunits<<<sms * 2, T, smem, st>>>(hdr, 2, nullptr, units, apos, A, bpos, B, mpos, M, (unsigned)unit_cap, cnt);
+        kunits<<<sms * 3, T, smem, st>>>(hdr, 2, nullptr, units, apos, A, bpos, B, mpos, M, (unsigned)unit_cap, cnt);
         CB_LAUNCH_CHECK();
         kslow<<<sms, T, smem, st>>>(hdr, 3, slow, nullptr, apos, A, bpos, B, mpos, M, (unsigned)unit_cap, cnt);
         CB_LAUNCH_CHECK();
     }
     {
         constexpr int T = 256;
-        const size_t smem = (sizeof(int32_t) << TC_MID_TAB) + (sizeof(uint32_t) << (TC_MID_BLOOM - 5));
-        tc_block_kernel<T, TC_MID_TAB, TC_MID_BLOOM, TC_MID_MAX, 0><<<sms * 8, T, smem, st>>>(
+        const size_t smem = sizeof(int32_t) << TC_MID_LOG2;
+        tc_block_kernel<T, TC_MID_LOG2, TC_MID_MAX, 0><<<sms * 6, T, smem, st>>>(
             hdr, 1, list1, nullptr, apos, A, bpos, B, mpos, M, (unsigned)unit_cap, cnt);
         CB_LAUNCH_CHECK();
     }
