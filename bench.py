@@ -194,7 +194,7 @@ class SpMM(Workload):
 
 class SpMV(SpMM):
     name = "spmv"
-    launches_per_step = 1
+    launches_per_step = 1     # one kernel below 2^20 stored entries, two (rows + long-row chunks) above
 
     def build(self):
         from comet_b200 import datasets

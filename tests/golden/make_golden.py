@@ -127,7 +127,9 @@ def parse_ta(path):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/COMET")
+    root = sys.argv[1]
     tdir = os.path.join(root, "test", "integration")
     out = {"source": "pnnl/COMET test/integration (CHECK lines and data/*.mtx)", "matrices": {},
            "cases": {}}
