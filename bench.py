@@ -469,6 +469,7 @@ def run_reference(args, w, rank):
     if rank != 0:
         return
     from oracle import oracle
+    oracle.use_all_cores()
     w.build()
     sample = w.cpu_setup()
     flops = getattr(w, "cpu_flops", w.flops)
@@ -624,6 +625,7 @@ def main():
     if not args.no_cpu and world == 1:
         sample = w.cpu_setup()
         from oracle import oracle
+        oracle.use_all_cores()
         flops = getattr(w, "cpu_flops", w.flops)
         w.cpu_step()
         t0 = time.perf_counter()

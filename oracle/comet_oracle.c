@@ -50,6 +50,15 @@ ORACLE_API int oracle_num_threads(void)
 #endif
 }
 
+ORACLE_API void oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------------- */
 /* MatrixMarket reader: SparseUtils.cpp:145-356 (CooMatrix::InitMarket)       */
 /* ------------------------------------------------------------------------- */

@@ -56,6 +56,14 @@ def num_threads():
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores():
+    """Launchers such as torch.distributed.run export OMP_NUM_THREADS=1; the CPU baseline is meant
+    to use every core of the host, so set the team size explicitly."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def _i64(a):
     return np.ascontiguousarray(a, dtype=np.int64)
 
