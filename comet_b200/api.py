@@ -24,14 +24,19 @@ import numpy as np
 from . import _lib
 from ._lib import MemRef1D, MemRef2D
 
-PLUS_TIMES = 0
-PLUS_PAIR = 1
+PLUS_TIMES, PLUS_PAIR, PLUS_FIRST, PLUS_SECOND, MIN_PLUS, MIN_FIRST, MIN_SECOND, ANY_PAIR = range(8)
 MASK_NONE = 0
 MASK_PUSH = 1
 
 _FMT = {"CSR": (0, 1), "DCSR": (1, 1), "COO": (2, 3)}
-_SEMIRINGS = {"+,*": PLUS_TIMES, "plusxy_times": PLUS_TIMES, "+,pair": PLUS_PAIR,
-              "plusxy_pairxy": PLUS_PAIR, PLUS_TIMES: PLUS_TIMES, PLUS_PAIR: PLUS_PAIR}
+# DSL / cometpy spellings (frontends/comet_dsl/mlir/MLIRGen.cpp:102-145) and the IR attribute strings
+_SEMIRINGS = {"+,*": PLUS_TIMES, "plusxy_times": PLUS_TIMES, "+,pair": PLUS_PAIR, "plusxy_pairxy": PLUS_PAIR,
+              "+,first": PLUS_FIRST, "plusxy_first": PLUS_FIRST, "+,second": PLUS_SECOND,
+              "plusxy_second": PLUS_SECOND, "min,+": MIN_PLUS, "minxy_plusxy": MIN_PLUS,
+              "min,first": MIN_FIRST, "minxy_first": MIN_FIRST, "min,second": MIN_SECOND,
+              "minxy_second": MIN_SECOND, "any,pair": ANY_PAIR, "any_pairxy": ANY_PAIR}
+_SEMIRINGS.update({c: c for c in range(8)})
+_DENSE_OUTPUT_SEMIRINGS = (PLUS_TIMES, PLUS_PAIR)
 
 
 class SparseTensor:
@@ -161,8 +166,15 @@ def _semiring(s):
         return PLUS_TIMES
     key = s.replace(" ", "") if isinstance(s, str) else s
     if key not in _SEMIRINGS:
-        raise ValueError("unsupported semiring %r (plus-times and plus-pair are handled)" % (s,))
+        raise ValueError("unsupported semiring %r" % (s,))
     return _SEMIRINGS[key]
+
+
+def _dense_semiring(s):
+    code = _semiring(s)
+    if code not in _DENSE_OUTPUT_SEMIRINGS:
+        raise ValueError("unsupported semiring %r for a dense result (plus-times and plus-pair are handled)" % (s,))
+    return code
 
 
 def spmv(A, x, y0=None, semiring=PLUS_TIMES):
@@ -173,7 +185,7 @@ def spmv(A, x, y0=None, semiring=PLUS_TIMES):
     x = _f64(x)
     y = np.zeros(A.nrows) if y0 is None else _f64(y0).copy()
     fn, _, (A,) = _entry(lib, "spmv", A)
-    fn(*pk.sparse(A), *pk.m1(x), *pk.m1(y), _semiring(semiring), 0 if y0 is None else 1)
+    fn(*pk.sparse(A), *pk.m1(x), *pk.m1(y), _dense_semiring(semiring), 0 if y0 is None else 1)
     _lib.check()
     return y
 
@@ -186,7 +198,7 @@ def spmm(A, B, C0=None, semiring=PLUS_TIMES):
     B = _f64(B)
     C = np.zeros((A.nrows, B.shape[1])) if C0 is None else _f64(C0).copy()
     fn, _, (A,) = _entry(lib, "spmm", A)
-    fn(*pk.sparse(A), *pk.m2(B), *pk.m2(C), _semiring(semiring), 0 if C0 is None else 1)
+    fn(*pk.sparse(A), *pk.m2(B), *pk.m2(C), _dense_semiring(semiring), 0 if C0 is None else 1)
     _lib.check()
     return C
 

@@ -42,7 +42,7 @@ struct Plan {
     int64_t nrows, ncols, nnz_b;
     const int64_t *apos, *acrd, *bpos, *bcrd, *mpos, *mcrd;
     const double *aval, *bval;
-    int pair;
+    int semi;                // semiring code
     int64_t *cpos;           // caller's array
     int64_t nnz_c;
     // owned device memory
@@ -111,6 +111,45 @@ __device__ __forceinline__ bool in_mask(const int64_t *__restrict__ mcrd, int64_
         if (v < j) ms = mid + 1; else me = mid;
     }
     return false;
+}
+
+// --------------------------------------------------------------------------
+// Semiring arithmetic (codes of include/comet_b200.h).  The second operator
+// combines A[i,k] and B[k,j]; the first one folds the products of one output.
+// "any" is only offered with "pair", where every product is 1, so it can share
+// the min fold.
+// --------------------------------------------------------------------------
+__device__ __forceinline__ double sr_combine(int semi, double a, double b)
+{
+    switch (semi) {
+    case COMET_B200_PLUS_PAIR: case COMET_B200_ANY_PAIR: return 1.0;
+    case COMET_B200_PLUS_FIRST: case COMET_B200_MIN_FIRST: return a;
+    case COMET_B200_PLUS_SECOND: case COMET_B200_MIN_SECOND: return b;
+    case COMET_B200_MIN_PLUS: return a + b;
+    default: return a * b;
+    }
+}
+
+__host__ __device__ __forceinline__ bool sr_is_min(int semi) { return semi >= COMET_B200_MIN_PLUS; }
+
+__device__ __forceinline__ double sr_identity(int semi) { return sr_is_min(semi) ? __longlong_as_double(0x7ff0000000000000LL) : 0.0; }
+
+// min fold on an f64 in shared or global memory (there is no native one)
+__device__ __forceinline__ void atomic_min_f64(double *addr, double v)
+{
+    unsigned long long *a = (unsigned long long *)addr;
+    unsigned long long old = *a;
+    while (v < __longlong_as_double((long long)old)) {
+        const unsigned long long assumed = old;
+        old = atomicCAS(a, assumed, (unsigned long long)__double_as_longlong(v));
+        if (old == assumed) break;
+    }
+}
+
+__device__ __forceinline__ void sr_fold(int semi, double *addr, double v)
+{
+    if (sr_is_min(semi)) atomic_min_f64(addr, v);
+    else atomicAdd(addr, v);
 }
 
 // --------------------------------------------------------------------------
@@ -195,7 +234,7 @@ hash_rows_kernel(unsigned nlist, const int32_t *__restrict__ list, const int64_t
                  const int64_t *__restrict__ acrd, const double *__restrict__ aval,
                  const int64_t *__restrict__ bpos, const int32_t *__restrict__ bcrd,
                  const double *__restrict__ bval, const int64_t *__restrict__ mpos,
-                 const int64_t *__restrict__ mcrd, int pair, int64_t *__restrict__ cnt,
+                 const int64_t *__restrict__ mcrd, int semi, int64_t *__restrict__ cnt,
                  const int64_t *__restrict__ cpos, int64_t *__restrict__ ccrd,
                  double *__restrict__ cval)
 {
@@ -210,7 +249,7 @@ hash_rows_kernel(unsigned nlist, const int32_t *__restrict__ list, const int64_t
         const int64_t r = list[it];
         for (int s = lane; s < HASH_SLOTS; s += 32) {
             keys[s] = -1;
-            if (NUMERIC) s_vals[w][s] = 0.0;
+            if (NUMERIC) s_vals[w][s] = sr_identity(semi);
         }
         __syncwarp();
         int64_t ms = 0, me = 0;
@@ -225,7 +264,7 @@ hash_rows_kernel(unsigned nlist, const int32_t *__restrict__ list, const int64_t
                 bool fresh;
                 int h = hash_insert(keys, j, &fresh);
                 fresh_count += fresh ? 1 : 0;
-                if (NUMERIC && h >= 0) atomicAdd(&s_vals[w][h], pair ? 1.0 : av * bval[q]);
+                if (NUMERIC && h >= 0) sr_fold(semi, &s_vals[w][h], sr_combine(semi, av, bval[q]));
             }
         }
         __syncwarp();
@@ -334,7 +373,7 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
                       const int64_t *__restrict__ acrd, const double *__restrict__ aval,
                       const int64_t *__restrict__ bpos, const int32_t *__restrict__ bcrd,
                       const double *__restrict__ bval, const int64_t *__restrict__ mpos,
-                      const int64_t *__restrict__ mcrd, int pair,
+                      const int64_t *__restrict__ mcrd, int semi,
                       const uint32_t *__restrict__ bm_store, const int64_t *__restrict__ cpos,
                       int64_t *__restrict__ ccrd, double *__restrict__ cval)
 {
@@ -383,7 +422,7 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
                 run++;
             }
         }
-        for (int64_t t = threadIdx.x; t < rown; t += BM_THREADS) cval[base + t] = 0.0;
+        for (int64_t t = threadIdx.x; t < rown; t += BM_THREADS) cval[base + t] = sr_identity(semi);
         __syncthreads();
         // accumulate every product at the rank of its column
         for (int64_t p = apos[r] + warp; p < apos[r + 1]; p += BM_THREADS / 32) {
@@ -395,7 +434,7 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
                 uint32_t bit = 1u << (j & 31);
                 if (!(word & bit)) continue;   // filtered out by the mask
                 unsigned rank = pre[j >> 5] + __popc(word & (bit - 1u));
-                atomicAdd(&cval[base + rank], pair ? 1.0 : av * bval[q]);
+                sr_fold(semi, &cval[base + rank], sr_combine(semi, av, bval[q]));
             }
         }
         __syncthreads();
@@ -475,7 +514,7 @@ int spgemm_symbolic(int64_t nrows, int64_t ncols_b, int64_t nnz_b, const int64_t
     memset(p, 0, sizeof(Plan));
     p->kind = 0; p->nrows = nrows; p->ncols = ncols_b; p->nnz_b = nnz_b;
     p->apos = apos; p->acrd = acrd; p->aval = aval; p->bpos = bpos; p->bcrd = bcrd; p->bval = bval;
-    p->mpos = mpos; p->mcrd = mpos ? mcrd : nullptr; p->pair = semiring == COMET_B200_PLUS_PAIR;
+    p->mpos = mpos; p->mcrd = mpos ? mcrd : nullptr; p->semi = semiring;
     p->cpos = cpos;
     p->words = (int)ceil_div(ncols_b, 32);
     int rc = 0;
@@ -502,7 +541,7 @@ int spgemm_symbolic(int64_t nrows, int64_t ncols_b, int64_t nnz_b, const int64_t
         unsigned cap = (unsigned)sm_count() * 16;
         if (grid > cap) grid = cap;
         hash_rows_kernel<false><<<grid, HASH_WARPS * 32, 0, st>>>(
-            p->n1, p->list1, apos, acrd, aval, bpos, p->bcrd32, bval, mpos, p->mcrd, p->pair, p->cnt,
+            p->n1, p->list1, apos, acrd, aval, bpos, p->bcrd32, bval, mpos, p->mcrd, p->semi, p->cnt,
             nullptr, nullptr, nullptr);
         STEP_CUDA(cudaGetLastError());
     }
@@ -588,7 +627,7 @@ int sparse_out_numeric(int64_t handle, int64_t *ccrd, double *cval, int keep, cu
             if (grid > cap) grid = cap;
             hash_rows_kernel<true><<<grid, HASH_WARPS * 32, 0, st>>>(
                 p->n1, p->list1, p->apos, p->acrd, p->aval, p->bpos, p->bcrd32, p->bval, p->mpos,
-                p->mcrd, p->pair, nullptr, p->cpos, ccrd, cval);
+                p->mcrd, p->semi, nullptr, p->cpos, ccrd, cval);
             if (cudaGetLastError() != cudaSuccess) rc = fail("spgemm numeric (hash) launch failed");
         }
         if (!rc && p->n2) {
@@ -599,7 +638,7 @@ int sparse_out_numeric(int64_t handle, int64_t *ccrd, double *cval, int keep, cu
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 bitmap_numeric_kernel<true><<<grid, BM_THREADS, smem, st>>>(
                     p->n2, p->list2, p->words, nullptr, p->apos, p->acrd, p->aval, p->bpos, p->bcrd32,
-                    p->bval, p->mpos, p->mcrd, p->pair, p->bm_store, p->cpos, ccrd, cval);
+                    p->bval, p->mpos, p->mcrd, p->semi, p->bm_store, p->cpos, ccrd, cval);
             } else {
                 int grid = bitmap_grid(p->n2, 0);
                 void *gbm = nullptr;
@@ -607,7 +646,7 @@ int sparse_out_numeric(int64_t handle, int64_t *ccrd, double *cval, int keep, cu
                 if (!rc)
                     bitmap_numeric_kernel<false><<<grid, BM_THREADS, 0, st>>>(
                         p->n2, p->list2, p->words, (uint32_t *)gbm, p->apos, p->acrd, p->aval, p->bpos,
-                        p->bcrd32, p->bval, p->mpos, p->mcrd, p->pair, p->bm_store, p->cpos, ccrd, cval);
+                        p->bcrd32, p->bval, p->mpos, p->mcrd, p->semi, p->bm_store, p->cpos, ccrd, cval);
             }
             if (!rc && cudaGetLastError() != cudaSuccess) rc = fail("spgemm numeric (bitmap) launch failed");
         }
@@ -635,7 +674,7 @@ int32_t comet_b200_dev_spgemm_symbolic_f64_i64(int64_t nrows, int64_t ncols_b, i
                                                int64_t *handle_out, void *stream)
 {
     cb200::clear_error();
-    if (semiring != COMET_B200_PLUS_TIMES && semiring != COMET_B200_PLUS_PAIR)
+    if (semiring < COMET_B200_PLUS_TIMES || semiring > COMET_B200_ANY_PAIR)
         return cb200::fail("spgemm: unsupported semiring %d", semiring);
     return cb200::spgemm_symbolic(nrows, ncols_b, nnz_b, apos, acrd, aval, bpos, bcrd, bval, mpos, mcrd,
                                   semiring, cpos, nnz_host, handle_out, (cudaStream_t)stream);

@@ -58,6 +58,14 @@ extern "C" {
    lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:198-361) */
 #define COMET_B200_PLUS_TIMES 0
 #define COMET_B200_PLUS_PAIR 1
+/* further semirings, taken by the sparse x sparse product only (the ones COMET tests on
+   CSR x CSR: test/integration/semiring/mm_Semiring*_CSRxCSR_oCSR.ta) */
+#define COMET_B200_PLUS_FIRST 2
+#define COMET_B200_PLUS_SECOND 3
+#define COMET_B200_MIN_PLUS 4
+#define COMET_B200_MIN_FIRST 5
+#define COMET_B200_MIN_SECOND 6
+#define COMET_B200_ANY_PAIR 7
 
 /* MaskType of ta.mul (include/comet/Dialect/TensorAlgebra/IR/TAOps.td:348-433) */
 #define COMET_B200_MASK_NONE 0

@@ -35,7 +35,9 @@
 
 #define ORACLE_API __attribute__((visibility("default")))
 
-enum { SEMIRING_PLUS_TIMES = 0, SEMIRING_PLUS_PAIR = 1 };
+/* semiring codes shared with include/comet_b200.h */
+enum { SEMIRING_PLUS_TIMES = 0, SEMIRING_PLUS_PAIR = 1, SEMIRING_PLUS_FIRST = 2, SEMIRING_PLUS_SECOND = 3,
+       SEMIRING_MIN_PLUS = 4, SEMIRING_MIN_FIRST = 5, SEMIRING_MIN_SECOND = 6, SEMIRING_ANY_PAIR = 7 };
 
 /* readMode values of comet_read(id, mode): lib/ExecutionEngine/SparseUtils.cpp:50-64 */
 enum { READ_DEFAULT = 1, READ_LOWER_TRI_STRICT = 2, READ_LOWER_TRI = 3,
@@ -293,9 +295,27 @@ ORACLE_API int oracle_reader_fill(void *h, int a1fmt, int a2fmt, int mode,
 /* inner sparse loops sequential in position order (IndexTreeToSCF.cpp:667-700)*/
 /* ------------------------------------------------------------------------- */
 
+/* second operator of the semiring (getSemiringSecondVal, IndexTreeToSCF.cpp:198-305) */
 static inline double combine(int semiring, double a, double b)
 {
-    return semiring == SEMIRING_PLUS_PAIR ? 1.0 : a * b;
+    switch (semiring) {
+    case SEMIRING_PLUS_PAIR: case SEMIRING_ANY_PAIR: return 1.0;
+    case SEMIRING_PLUS_FIRST: case SEMIRING_MIN_FIRST: return a;
+    case SEMIRING_PLUS_SECOND: case SEMIRING_MIN_SECOND: return b;
+    case SEMIRING_MIN_PLUS: return a + b;
+    default: return a * b;
+    }
+}
+
+/* first operator (getSemiringFirstVal, :307-361): plusxy adds, minxy is select(old < v, old, v),
+   any takes the new value */
+static inline double reduce(int semiring, double old, double v)
+{
+    switch (semiring) {
+    case SEMIRING_MIN_PLUS: case SEMIRING_MIN_FIRST: case SEMIRING_MIN_SECOND: return old < v ? old : v;
+    case SEMIRING_ANY_PAIR: return v;
+    default: return old + v;
+    }
 }
 
 ORACLE_API void oracle_spmv_csr(int64_t nrows, const int64_t *pos, const int64_t *crd,
@@ -516,7 +536,7 @@ ORACLE_API void oracle_spgemm_numeric(int64_t nrows, int64_t ncols, const int64_
                 int64_t j = bcrd[q];
                 if (mask && !mask[j]) continue;
                 double v = combine(semiring, av, bval[q]);
-                if (mark[j] == mark_value) ws[j] = ws[j] + v;
+                if (mark[j] == mark_value) ws[j] = reduce(semiring, ws[j], v);
                 else { mark[j] = mark_value; list[num++] = j; ws[j] = v; }
             }
         }

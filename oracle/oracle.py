@@ -17,8 +17,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libcomet_oracle.so")
 
-PLUS_TIMES = 0
-PLUS_PAIR = 1
+PLUS_TIMES, PLUS_PAIR, PLUS_FIRST, PLUS_SECOND, MIN_PLUS, MIN_FIRST, MIN_SECOND, ANY_PAIR = range(8)
 
 # runtime format codes: include/comet/ExecutionEngine/RunnerUtils.h:71-77
 DENSE, CU, CN, S = 0, 1, 2, 3

@@ -56,6 +56,12 @@ CASES = {
     "ops/mult_spgemm_CSRxCSR_oCSR_wMasking.ta": "spgemm_masked",
     "semiring/mm_SemiringPlusTimes_CSRxCSR_oCSR.ta": "spgemm",
     "semiring/mm_SemiringPlusPair_CSRxCSR_oCSR.ta": "spgemm",
+    "semiring/mm_SemiringPlusFirst_CSRxCSR_oCSR.ta": "spgemm",
+    "semiring/mm_SemiringPlusSecond_CSRxCSR_oCSR.ta": "spgemm",
+    "semiring/mm_SemiringMinPlus_CSRxCSR_oCSR.ta": "spgemm",
+    "semiring/mm_SemiringMinFirst_CSRxCSR_oCSR.ta": "spgemm",
+    "semiring/mm_SemiringMinSecond_CSRxCSR_oCSR.ta": "spgemm",
+    "semiring/mm_SemiringAnyPair_CSRxCSR_oCSR.ta": "spgemm",
     # reductions / triangle counting
     "ops/sum_CSR.ta": "sum",
     "ops/sum_COO.ta": "sum",

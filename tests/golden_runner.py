@@ -29,7 +29,10 @@ def run_case(case, mtx_dir, backend):
         read[name] = oracle.read_mtx(path, T[name]["format"], r["read_mode"])
     fills = case["fills"]
     kind = case["kind"]
-    semiring = oracle.PLUS_PAIR if case["semiring"] == "+,pair" else oracle.PLUS_TIMES
+    semiring = {None: oracle.PLUS_TIMES, "*": oracle.PLUS_TIMES, "+,*": oracle.PLUS_TIMES,
+                "+,pair": oracle.PLUS_PAIR, "+,first": oracle.PLUS_FIRST, "+,second": oracle.PLUS_SECOND,
+                "min,+": oracle.MIN_PLUS, "min,first": oracle.MIN_FIRST, "min,second": oracle.MIN_SECOND,
+                "any,pair": oracle.ANY_PAIR}[case["semiring"]]
 
     if kind == "reader":
         return _print_sparse(next(iter(read.values())))

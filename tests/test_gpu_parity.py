@@ -365,3 +365,28 @@ def test_spmv_large_power_law_uses_the_chunk_list():
     _close(api.spmv(A, x), oracle.spmv(_orc(A), x), scale)
     _close(api.spmv(A, x, y0), oracle.spmv(_orc(A), x, y0), scale)
     assert np.array_equal(api.spmv(A, x, semiring=api.PLUS_PAIR), np.diff(A.a2pos).astype(np.float64))
+
+
+@pytest.mark.parametrize("semiring", ["+,first", "+,second", "min,+", "min,first", "min,second", "any,pair"])
+def test_spgemm_further_semirings(semiring):
+    """The other semirings COMET tests on CSR x CSR: structure identical, min / any results exact,
+    plus results within tolerance; rows short enough for the hash path and long enough for the bitmap path."""
+    code = api._semiring(semiring)
+    A = datasets.rmat_csr(11, 8, seed=21)
+    A.val[:] = datasets.dense_uniform(A.nnz, 22, -2.0, 3.0)
+    got = api.spgemm(A, A, None, semiring)
+    ref = oracle.spgemm(_orc(A), _orc(A), None, code)
+    assert np.array_equal(got.a2pos, ref.a2pos) and np.array_equal(got.a2crd, ref.a2crd)
+    if semiring.startswith("+"):
+        _close(got.val, ref.val, oracle.spgemm(_abs(A), _abs(A), None, code).val)
+    else:
+        assert np.array_equal(got.val, ref.val)
+    # with a push mask as well
+    M = datasets.rmat_csr(11, 16, seed=23)
+    gm = api.spgemm(A, A, M, semiring)
+    rm = oracle.spgemm(_orc(A), _orc(A), _orc(M), code)
+    assert np.array_equal(gm.a2pos, rm.a2pos) and np.array_equal(gm.a2crd, rm.a2crd)
+    if semiring.startswith("+"):
+        _close(gm.val, rm.val, oracle.spgemm(_abs(A), _abs(A), _orc(M), code).val)
+    else:
+        assert np.array_equal(gm.val, rm.val)
