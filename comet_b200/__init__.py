@@ -7,6 +7,6 @@ operations, behind a C ABI that takes COMET's pos/crd/val memref descriptors.
     comet_b200.datasets seeded synthetic inputs of the benchmark configurations
     comet_b200.build    in-tree nvcc build of libcomet_b200.so
 """
-from .api import (ANY_PAIR, MIN_FIRST, MIN_PLUS, MIN_SECOND, PLUS_FIRST, PLUS_PAIR, PLUS_SECOND, PLUS_TIMES, SparseTensor, einsum, elews_csr_csr,  # noqa: F401
+from .api import (ANY_PAIR, MIN_FIRST, MIN_PLUS, MIN_SECOND, PLUS_FIRST, PLUS_PAIR, PLUS_SECOND, PLUS_TIMES, SparseTensor, dense_times_sparse, einsum, elews_csr_csr,  # noqa: F401
                   elews_sparse_dense, masked_pair_count, reduce_sum, sddmm, spgemm, spmm, spmv,
                   triangle_count)

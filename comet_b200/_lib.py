@@ -29,6 +29,7 @@ SIGNATURES = {
     "comet_b200_spmv_f64_i64": (None, _SPARSE + _MEMREF * 2 + [c_int32, c_int32]),
     "comet_b200_spmm_f64_i64": (None, _SPARSE + _MEMREF * 2 + [c_int32, c_int32]),
     "comet_b200_sddmm_f64_i64": (None, _SPARSE + _MEMREF * 2 + _SPARSE),
+    "comet_b200_dense_times_sparse_f64_i64": (None, _MEMREF + _SPARSE + _MEMREF + [c_int32, c_int32]),
     "comet_b200_elews_mul_sparse_dense_f64_i64": (None, _SPARSE + _MEMREF + _SPARSE),
     "comet_b200_spgemm_symbolic_f64_i64": (c_int64, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF * 2),
     "comet_b200_spgemm_numeric_f64_i64": (None, [c_int64] + _MEMREF * 2),
@@ -45,6 +46,8 @@ SIGNATURES = {
                                               c_int32, c_int32, c_int32, c_void_p]),
     "comet_b200_dev_spmm_noalloc_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 5 + [c_int64, c_void_p, c_int64,
                                                       c_int32, c_int32, c_void_p]),
+    "comet_b200_dev_dense_times_sparse_f64_i64": (c_int32, [c_int64] * 4 + [c_void_p] * 5 + [c_int64, c_void_p, c_int64,
+                                                            c_int32, c_int32, c_void_p]),
     "comet_b200_dev_sddmm_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 4 + [c_int64, c_void_p, c_int64,
                                                c_void_p, c_void_p]),
     "comet_b200_dev_transpose_f64": (c_int32, [c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),

@@ -203,6 +203,23 @@ def spmm(A, B, C0=None, semiring=PLUS_TIMES):
     return C
 
 
+def dense_times_sparse(A, B, C0=None, semiring=PLUS_TIMES):
+    """C = C0 + A @ B with dense A (vector or row-major matrix) and sparse B (CSR, DCSR or COO):
+    the `dense @ sparse` forms of cometpy."""
+    B = as_sparse(B)
+    lib = _lib.load()
+    pk = _Packer()
+    A = _f64(A)
+    vec = A.ndim == 1
+    shape = (B.ncols,) if vec else (A.shape[0], B.ncols)
+    C = np.zeros(shape) if C0 is None else _f64(C0).reshape(shape).copy()
+    fn, _, (B,) = _entry(lib, "dense_times_sparse", B)
+    pack = pk.m1 if vec else pk.m2
+    fn(*pack(A), *pk.sparse(B), *pack(C), _dense_semiring(semiring), 0 if C0 is None else 1)
+    _lib.check()
+    return C
+
+
 def sddmm(S, X, Y, y_is_kj=False):
     """values of S .* (X @ Y^T) on S's pattern.  Y is [cols, K] row-major, or the
     [K, cols] operand D[k,j] of the reference's sddmm.ta when ``y_is_kj``."""
@@ -309,12 +326,19 @@ def einsum(subscripts, A, B, mask=None, mask_type="push", semiring="+,*"):
     spec = subscripts.replace(" ", "")
     lhs, out = spec.split("->")
     a, b = lhs.split(",")
-    if not (len(a) == 2 and a[1] == b[0]):
+    if not (a[-1] == b[0]):
         raise ValueError("unsupported einsum " + subscripts)
     if mask is not None and mask_type != "push":
         raise ValueError("only the push mask is handled")
     sr = _semiring(semiring)
+    sparse_a = hasattr(A, "format") or hasattr(A, "a2crd")
     sparse_b = hasattr(B, "format") or hasattr(B, "a2crd")
+    if not sparse_a and sparse_b:
+        ok = (len(a) == 1 and len(b) == 2 and a == b[0] and out == b[1]) or \
+             (len(a) == 2 and len(b) == 2 and out == a[0] + b[1])
+        if not ok:
+            raise ValueError("unsupported einsum " + subscripts)
+        return dense_times_sparse(A, B, semiring=sr)
     if len(b) == 1 and out == a[0]:
         return spmv(A, B, semiring=sr)
     if len(b) == 2 and out == a[0] + b[1]:

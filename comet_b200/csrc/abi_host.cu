@@ -512,6 +512,52 @@ static void elews_sd_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void 
     finish(st);
 }
 
+// Dense x sparse: A is a rank-1 (vector) or rank-2 row-major memref, C has the same rank.
+static void dense_sparse_impl(int isz, int64_t A_rank, void *A_ptr, COMET_B200_SPARSE2D(B), int64_t C_rank,
+                              void *C_ptr, int32_t semiring, int32_t accumulate)
+{
+    UNUSED_TILES(B);
+    clear_error();
+    HostSparse B;
+    if (GET_SPARSE("dense x sparse: B", B, &B)) return;
+    if (A_rank != C_rank || (A_rank != 1 && A_rank != 2)) { fail("dense x sparse: A and C must both be vectors or both matrices"); return; }
+    int64_t m, lda, ldc;
+    double *ha, *hc;
+    if (A_rank == 1) {
+        Arr a, c;
+        if (get1d("dense x sparse: A", A_rank, A_ptr, 8, &a) || get1d("dense x sparse: C", C_rank, C_ptr, 8, &c)) return;
+        if (a.n < B.nrows || c.n < B.ncols) { fail("dense x sparse: vector shorter than the matrix dimension"); return; }
+        m = 1; lda = B.nrows; ldc = B.ncols; ha = (double *)a.data; hc = (double *)c.data;
+    } else {
+        Mat a, c;
+        if (get2d("dense x sparse: A", A_rank, A_ptr, &a) || get2d("dense x sparse: C", C_rank, C_ptr, &c)) return;
+        if (a.cols < B.nrows || c.cols < B.ncols || c.rows < a.rows || (a.cols > 1 && a.s1 != 1) || (c.cols > 1 && c.s1 != 1)) {
+            fail("dense x sparse: A must be row-major [m, rows(B)] and C row-major [m, cols(B)]");
+            return;
+        }
+        m = a.rows; lda = a.s0; ldc = c.s0; ha = a.data; hc = c.data;
+    }
+    cudaStream_t st;
+    if (need_stream(&st)) return;
+    DevBag bag(st);
+    DevSparse dB;
+    if (upload_sparse("dense x sparse", B, bag, &dB)) return;
+    double *dA, *dC;
+    const size_t abytes = m > 0 ? (size_t)((m - 1) * lda + B.nrows) * 8 : 0;
+    const size_t cbytes = m > 0 ? (size_t)((m - 1) * ldc + B.ncols) * 8 : 0;
+    if (bag.upload((void **)&dA, ha, abytes)) return;
+    if (accumulate || ldc != B.ncols) { if (bag.upload((void **)&dC, hc, cbytes)) return; }
+    else if (bag.alloc((void **)&dC, cbytes)) return;
+    if (comet_b200_dev_dense_times_sparse_f64_i64(m, B.ncols, dB.nrows_k, B.nnz, dB.row_ids, dB.pos, dB.crd, dB.val, dA,
+                                                  lda, dC, ldc, semiring, accumulate, st))
+        return;
+    if (cbytes && cudaMemcpyAsync(hc, dC, cbytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+        fail("dense x sparse: copy of the result failed");
+        return;
+    }
+    finish(st);
+}
+
 static int64_t sparse_out_symbolic(int isz, int kind, const HostSparse &A, const HostSparse &B,
                                    const HostSparse *M, int semiring, Arr cpos, int64_t sizes_rank,
                                    void *sizes_ptr)
@@ -717,6 +763,10 @@ BOTH_WIDTHS(void, spmm, spmm_impl,
             (COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank, void *C_ptr, int32_t semiring,
              int32_t accumulate),
             FWD_SPARSE(A), B_rank, B_ptr, C_rank, C_ptr, semiring, accumulate)
+BOTH_WIDTHS(void, dense_times_sparse, dense_sparse_impl,
+            (int64_t A_rank, void *A_ptr, COMET_B200_SPARSE2D(B), int64_t C_rank, void *C_ptr, int32_t semiring,
+             int32_t accumulate),
+            A_rank, A_ptr, FWD_SPARSE(B), C_rank, C_ptr, semiring, accumulate)
 BOTH_WIDTHS(void, sddmm, sddmm_impl,
             (COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O)),
             FWD_SPARSE(S), X_rank, X_ptr, D_rank, D_ptr, FWD_SPARSE(O))

@@ -129,6 +129,15 @@ COMET_B200_EXPORT void comet_b200_spmm_f64_i64(COMET_B200_SPARSE2D(A), int64_t B
                                                int64_t C_rank, void *C_ptr, int32_t semiring,
                                                int32_t accumulate);
 
+/* C[a,c] = C[a,c] (+) sum_b A[a,b] (x) B[b,c] with dense A and C (both rank-1 vectors or both
+   row-major rank-2 matrices) and sparse B (CSR, DCSR or COO): the dense x sparse forms of ta.mul
+   (test/integration/ops/mult_Dense{Mat,Vec}x{CSR,DCSR,COO}.ta; loops a -> b -> c,
+   lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:476-489, 667-783). */
+COMET_B200_EXPORT void comet_b200_dense_times_sparse_f64_i64(int64_t A_rank, void *A_ptr,
+                                                             COMET_B200_SPARSE2D(B), int64_t C_rank,
+                                                             void *C_ptr, int32_t semiring,
+                                                             int32_t accumulate);
+
 /* O = S .* (X * D): O takes S's pos/crd, O.val[p] = S.val[p] * sum_k X[i,k] * D[k,j].
    X is a row-major [rows, K] memref; D is a 2-D memref of sizes {K, cols} whose
    strides select the layout: {ld, 1} is the D[k,j] operand of
@@ -208,6 +217,10 @@ COMET_B200_EXPORT void comet_b200_spmv_f64_i32(COMET_B200_SPARSE2D(A), int64_t x
 COMET_B200_EXPORT void comet_b200_spmm_f64_i32(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
                                                int64_t C_rank, void *C_ptr, int32_t semiring,
                                                int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_dense_times_sparse_f64_i32(int64_t A_rank, void *A_ptr,
+                                                             COMET_B200_SPARSE2D(B), int64_t C_rank,
+                                                             void *C_ptr, int32_t semiring,
+                                                             int32_t accumulate);
 COMET_B200_EXPORT void comet_b200_sddmm_f64_i32(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr,
                                                 int64_t D_rank, void *D_ptr,
                                                 COMET_B200_SPARSE2D(O));
@@ -276,6 +289,12 @@ COMET_B200_EXPORT int32_t comet_b200_dev_spmm_f64_i64(int64_t nrows, int64_t nco
 COMET_B200_EXPORT int32_t comet_b200_dev_spmm_noalloc_f64_i64(
     int64_t nrows, int64_t nnz, int64_t k, const int64_t *row_ids, const int64_t *pos,
     const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
+    int32_t semiring, int32_t accumulate, void *stream);
+
+/* c[m, ncols] (+)= a[m, rows(B)] * B for the nstored rows B holds (row_ids as above). */
+COMET_B200_EXPORT int32_t comet_b200_dev_dense_times_sparse_f64_i64(
+    int64_t m, int64_t ncols, int64_t nstored, int64_t nnz, const int64_t *row_ids, const int64_t *pos,
+    const int64_t *crd, const double *val, const double *a, int64_t lda, double *c, int64_t ldc,
     int32_t semiring, int32_t accumulate, void *stream);
 
 /* y is row-major [ncols, k] with leading dimension ldy. */

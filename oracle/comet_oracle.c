@@ -396,6 +396,26 @@ ORACLE_API void oracle_spmm_coo(int64_t k, const int64_t *a1pos, const int64_t *
     }
 }
 
+/* Dense x sparse: C[a,c] = C[a,c] + A[a,b] * B[b,c] with A dense (m rows; m = 1 for a vector) and B
+   sparse; loops a -> b -> c in label order, a parallel, b over the rows B stores, c over the row's
+   entries (test/integration/ops/mult_Dense{Mat,Vec}x{CSR,DCSR,COO}.ta).  `rows` (DCSR row
+   coordinates) may be NULL; for COO pass nstored = nnz, rows = row coordinates, pos = NULL. */
+ORACLE_API void oracle_dense_times_sparse(int64_t m, int64_t nstored, const int64_t *rows,
+                                          const int64_t *pos, const int64_t *crd, const double *val,
+                                          const double *a, int64_t lda, double *c, int64_t ldc, int semiring)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < m; i++) {
+        for (int64_t r = 0; r < nstored; r++) {
+            int64_t b = rows ? rows[r] : r;
+            int64_t s = pos ? pos[r] : r, e = pos ? pos[r + 1] : r + 1;
+            double av = a[i * lda + b];
+            for (int64_t p = s; p < e; p++)
+                c[i * ldc + crd[p]] = c[i * ldc + crd[p]] + combine(semiring, av, val[p]);
+        }
+    }
+}
+
 /* ------------------------------------------------------------------------- */
 /* SDDMM: out.val[p] = S.val[p] * sum_k X[i,k] * Y[j,k], k ascending, the sum  */
 /* starting from T = 0.0 (test/integration/kernels/sddmm.ta:24-30).  The       */

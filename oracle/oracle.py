@@ -157,6 +157,24 @@ def spmm(A, B, C0=None, semiring=PLUS_TIMES):
     return C
 
 
+def dense_times_sparse(A, B, C0=None, semiring=PLUS_TIMES):
+    """C = C0 + A @ B with dense A (vector or matrix) and sparse B (CSR / DCSR / COO)."""
+    A = _f64(A)
+    vec = A.ndim == 1
+    A2 = A.reshape(1, -1) if vec else A
+    m = A2.shape[0]
+    C = np.zeros((m, B.ncols)) if C0 is None else _f64(C0).reshape(m, B.ncols).copy()
+    if B.format == "CSR":
+        nst, rows, pos = B.nrows, None, _i64(B.a2pos)
+    elif B.format == "DCSR":
+        nst, rows, pos = int(B.a1pos[1]), _i64(B.a1crd), _i64(B.a2pos)
+    else:
+        nst, rows, pos = B.nnz, _i64(B.a1crd), None
+    lib().oracle_dense_times_sparse(_l(m), _l(nst), _p(rows), _p(pos), _p(_i64(B.a2crd)), _p(_f64(B.val)),
+                                    _p(A2), _l(A2.shape[1]), _p(C), _l(B.ncols), int(semiring))
+    return C[0] if vec else C
+
+
 def sddmm(S, X, Y, y_is_kj=False):
     """out.val = S.val * (X @ Y^T sampled on S).  ``Y`` is (ncols, K) row-major,
     or (K, ncols) row-major when ``y_is_kj`` (the D[k,j] operand of sddmm.ta)."""

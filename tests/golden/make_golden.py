@@ -44,6 +44,19 @@ CASES = {
     "semiring/mm_SemiringPlusTimes_CSRxDense_oDense.ta": "spmm",
     "semiring/mm_SemiringPlusTimes_DCSRxDense_oDense.ta": "spmm",
     "semiring/mm_SemiringPlusTimes_COOxDense_oDense.ta": "spmm",
+    # dense x sparse -> dense
+    "ops/mult_DenseMatxCSR.ta": "dense_sparse",
+    "ops/mult_DenseMatxDCSR.ta": "dense_sparse",
+    "ops/mult_DenseMatxCOO.ta": "dense_sparse",
+    "ops/mult_DenseVecxCSR.ta": "dense_sparse",
+    "ops/mult_DenseVecxDCSR.ta": "dense_sparse",
+    "ops/mult_DenseVecxCOO.ta": "dense_sparse",
+    "semiring/mm_SemiringPlusTimes_DensexCSR_oDense.ta": "dense_sparse",
+    "semiring/mm_SemiringPlusTimes_DensexDCSR_oDense.ta": "dense_sparse",
+    "semiring/mm_SemiringPlusTimes_DensexCOO_oDense.ta": "dense_sparse",
+    "semiring/mv_SemiringPlusTimes_DensexCSR_oDense.ta": "dense_sparse",
+    "semiring/mv_SemiringPlusTimes_DensexDCSR_oDense.ta": "dense_sparse",
+    "semiring/mv_SemiringPlusTimes_DensexCOO_oDense.ta": "dense_sparse",
     # sampled dense-dense
     "kernels/sddmm.ta": "sddmm",
     # elementwise

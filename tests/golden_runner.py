@@ -49,6 +49,16 @@ def run_case(case, mtx_dir, backend):
         B = np.full((A.ncols, k), fills["B"])
         C = backend.spmm(A, B, np.full((A.nrows, k), fills["C"]), semiring)
         return oracle.print_memref(C)
+    if kind == "dense_sparse":
+        B = read["B"]
+        a_labels = T["A"]["labels"]
+        if len(a_labels) == 1:
+            A = np.full(B.nrows, fills["A"])
+            C0 = np.full(B.ncols, fills["C"])
+        else:
+            A = np.full((case["index_sizes"][a_labels[0]], B.nrows), fills["A"])
+            C0 = np.full((A.shape[0], B.ncols), fills["C"])
+        return oracle.print_memref(backend.dense_times_sparse(A, B, C0, semiring))
     if kind == "sddmm":
         S = read["B"]
         k = case["index_sizes"]["k"]

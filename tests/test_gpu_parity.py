@@ -390,3 +390,21 @@ def test_spgemm_further_semirings(semiring):
         _close(gm.val, rm.val, oracle.spgemm(_abs(A), _abs(A), _orc(M), code).val)
     else:
         assert np.array_equal(gm.val, rm.val)
+
+
+@pytest.mark.parametrize("fmt", ["CSR", "DCSR", "COO"])
+def test_dense_times_sparse(fmt, tmp_path):
+    Bm = _skewed(400, seed=31)
+    path = tmp_path / "b.mtx"
+    datasets.write_mtx(str(path), Bm)
+    B = oracle.read_mtx(str(path), fmt)
+    x = datasets.dense_uniform(B.nrows, 1)
+    A = datasets.dense_uniform((13, B.nrows), 2)
+    absB = _abs(B)
+    _close(api.dense_times_sparse(x, B), oracle.dense_times_sparse(x, B), oracle.dense_times_sparse(np.abs(x), absB))
+    C0 = datasets.dense_uniform((13, B.ncols), 3)
+    _close(api.dense_times_sparse(A, B, C0), oracle.dense_times_sparse(A, B, C0),
+           oracle.dense_times_sparse(np.abs(A), absB, np.abs(C0)))
+    _close(api.einsum("ij,jk->ik", A, B), oracle.dense_times_sparse(A, B), oracle.dense_times_sparse(np.abs(A), absB))
+    assert np.array_equal(api.dense_times_sparse(x, B, semiring=api.PLUS_PAIR),
+                          oracle.dense_times_sparse(x, B, semiring=oracle.PLUS_PAIR))
