@@ -31,6 +31,7 @@ SIGNATURES = {
     "comet_b200_sddmm_f64_i64": (None, _SPARSE + _MEMREF * 2 + _SPARSE),
     "comet_b200_dense_times_sparse_f64_i64": (None, _MEMREF + _SPARSE + _MEMREF + [c_int32, c_int32]),
     "comet_b200_elews_mul_sparse_dense_f64_i64": (None, _SPARSE + _MEMREF + _SPARSE),
+    "comet_b200_elews_mul_sparse_dense_to_dense_f64_i64": (None, _SPARSE + _MEMREF * 2),
     "comet_b200_spgemm_symbolic_f64_i64": (c_int64, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF * 2),
     "comet_b200_spgemm_numeric_f64_i64": (None, [c_int64] + _MEMREF * 2),
     "comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64": (c_int64, _SPARSE * 2 + _MEMREF * 2),
@@ -53,6 +54,8 @@ SIGNATURES = {
     "comet_b200_dev_transpose_f64": (c_int32, [c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "comet_b200_dev_elews_mul_sparse_dense_f64_i64": (c_int32, [c_int64, c_int64] + [c_void_p] * 5 +
                                                       [c_int64, c_void_p, c_void_p]),
+    "comet_b200_dev_elews_mul_sparse_dense_to_dense_f64_i64": (c_int32, [c_int64, c_int64] + [c_void_p] * 6 +
+                                                               [c_int64, c_void_p, c_int64, c_void_p]),
     "comet_b200_dev_spgemm_symbolic_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 8 + [c_int32, c_void_p,
                                                          POINTER(c_int64), POINTER(c_int64), c_void_p]),
     "comet_b200_dev_elews_mul_sparse_sparse_symbolic_f64_i64": (c_int32, [c_int64] + [c_void_p] * 7 +

@@ -251,6 +251,19 @@ def elews_sparse_dense(A, B):
     return out.val
 
 
+def elews_sparse_dense_to_dense(A, B, C0=None):
+    """Dense C with A.val * B at A's stored positions (A CSR, DCSR or COO), C0 (default zeros) elsewhere."""
+    A = as_sparse(A)
+    lib = _lib.load()
+    pk = _Packer()
+    B = _f64(B)
+    C = np.zeros((A.nrows, A.ncols)) if C0 is None else _f64(C0).copy()
+    fn, _, (A,) = _entry(lib, "elews_mul_sparse_dense_to_dense", A)
+    fn(*pk.sparse(A), *pk.m2(B), *pk.m2(C))
+    _lib.check()
+    return C
+
+
 def _finish_sparse_out(lib, handle, nrows, ncols, cpos, sizes):
     _lib.check()
     nnz = int(sizes[8])

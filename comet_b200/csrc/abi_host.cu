@@ -512,6 +512,49 @@ static void elews_sd_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void 
     finish(st);
 }
 
+// C (dense) = A (sparse) .* B (dense): products land at A's stored positions, the rest of C keeps its values.
+static void elews_to_dense_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank,
+                                void *C_ptr)
+{
+    UNUSED_TILES(A);
+    clear_error();
+    HostSparse A;
+    Mat B, C;
+    if (GET_SPARSE("elews_mul: A", A, &A)) return;
+    if (get2d("elews_mul: B", B_rank, B_ptr, &B) || get2d("elews_mul: C", C_rank, C_ptr, &C)) return;
+    if (B.rows < A.nrows || B.cols < A.ncols || C.rows < A.nrows || C.cols < A.ncols || (B.cols > 1 && B.s1 != 1) ||
+        (C.cols > 1 && C.s1 != 1)) {
+        fail("elews_mul: B and C must be row-major [rows, cols]");
+        return;
+    }
+    cudaStream_t st;
+    if (need_stream(&st)) return;
+    DevBag bag(st);
+    DevSparse dA;
+    memset(&dA, 0, sizeof(dA));
+    if (bag.upload_idx(&dA.crd, A.a2crd, A.nnz, A.isz)) return;
+    if (bag.upload((void **)&dA.val, A.val, (size_t)A.nnz * 8)) return;
+    int64_t nstored = A.nrows;
+    if (A.fmt == F_COO) { if (bag.upload_idx(&dA.rows, A.a1crd, A.nnz, A.isz)) return; }
+    else {
+        nstored = A.nstored;
+        if (bag.upload_idx(&dA.pos, A.a2pos, nstored + 1, A.isz)) return;
+        if (A.fmt == F_DCSR && bag.upload_idx(&dA.row_ids, A.a1crd, nstored, A.isz)) return;
+    }
+    double *dB, *dC;
+    const size_t bbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * B.s0 + A.ncols) * 8 : 0;
+    const size_t cbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * C.s0 + A.ncols) * 8 : 0;
+    if (bag.upload((void **)&dB, B.data, bbytes) || bag.upload((void **)&dC, C.data, cbytes)) return;
+    if (comet_b200_dev_elews_mul_sparse_dense_to_dense_f64_i64(nstored, A.nnz, dA.row_ids, dA.pos, dA.rows, dA.crd,
+                                                               dA.val, dB, B.s0, dC, C.s0, st))
+        return;
+    if (cbytes && cudaMemcpyAsync(C.data, dC, cbytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+        fail("elews_mul: copy of the result failed");
+        return;
+    }
+    finish(st);
+}
+
 // Dense x sparse: A is a rank-1 (vector) or rank-2 row-major memref, C has the same rank.
 static void dense_sparse_impl(int isz, int64_t A_rank, void *A_ptr, COMET_B200_SPARSE2D(B), int64_t C_rank,
                               void *C_ptr, int32_t semiring, int32_t accumulate)
@@ -773,6 +816,9 @@ BOTH_WIDTHS(void, sddmm, sddmm_impl,
 BOTH_WIDTHS(void, elews_mul_sparse_dense, elews_sd_impl,
             (COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, COMET_B200_SPARSE2D(C)),
             FWD_SPARSE(A), B_rank, B_ptr, FWD_SPARSE(C))
+BOTH_WIDTHS(void, elews_mul_sparse_dense_to_dense, elews_to_dense_impl,
+            (COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank, void *C_ptr),
+            FWD_SPARSE(A), B_rank, B_ptr, C_rank, C_ptr)
 BOTH_WIDTHS(int64_t, spgemm_symbolic, spgemm_symbolic_impl,
             (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
              int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr),

@@ -155,6 +155,14 @@ COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_f64_i64(COMET_B200_SPAR
                                                                  int64_t B_rank, void *B_ptr,
                                                                  COMET_B200_SPARSE2D(C));
 
+/* C = A .* B with sparse A (CSR, DCSR or COO), dense row-major B and a DENSE row-major C: the
+   products are assigned at A's stored positions, every other element of C keeps its value
+   (test/integration/ops/eltwise_mult_{CSR,DCSR}xDense_oDense.ta, eltwise_mult_DensexCSR_oDense.ta;
+   the multiplication commutes, so dense .* sparse is the same call). */
+COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_to_dense_f64_i64(COMET_B200_SPARSE2D(A),
+                                                                          int64_t B_rank, void *B_ptr,
+                                                                          int64_t C_rank, void *C_ptr);
+
 /* Sparse-output operations use the two-call protocol COMET already uses for
    file input (read_input_sizes_2D_f64 then read_input_2D_f64_i64,
    lib/Dialect/TensorAlgebra/Transforms/TensorDeclLowering.cpp:937-1052): the
@@ -227,6 +235,9 @@ COMET_B200_EXPORT void comet_b200_sddmm_f64_i32(COMET_B200_SPARSE2D(S), int64_t 
 COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_f64_i32(COMET_B200_SPARSE2D(A),
                                                                  int64_t B_rank, void *B_ptr,
                                                                  COMET_B200_SPARSE2D(C));
+COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_to_dense_f64_i32(COMET_B200_SPARSE2D(A),
+                                                                          int64_t B_rank, void *B_ptr,
+                                                                          int64_t C_rank, void *C_ptr);
 COMET_B200_EXPORT int64_t comet_b200_spgemm_symbolic_f64_i32(
     COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
     int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr);
@@ -314,6 +325,13 @@ COMET_B200_EXPORT int32_t comet_b200_dev_transpose_f64(int64_t rows, int64_t col
 COMET_B200_EXPORT int32_t comet_b200_dev_elews_mul_sparse_dense_f64_i64(
     int64_t nrows, int64_t nnz, const int64_t *pos, const int64_t *rows, const int64_t *crd,
     const double *val, const double *b, int64_t ldb, double *out, void *stream);
+
+/* Dense-output form: c[row, col] = val * b[row, col] at the stored positions (pos/row_ids for CSR/DCSR
+   with nstored rows, or rows != NULL for COO). */
+COMET_B200_EXPORT int32_t comet_b200_dev_elews_mul_sparse_dense_to_dense_f64_i64(
+    int64_t nstored, int64_t nnz, const int64_t *row_ids, const int64_t *pos, const int64_t *rows,
+    const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
+    void *stream);
 
 /* Sparse-output operations on device arrays.  *handle_out receives a handle,
    cpos[nrows+1] is filled, *nnz_host (host memory) receives nnz(C) after an

@@ -204,6 +204,23 @@ def elews_sparse_dense(A, B):
     return out
 
 
+def elews_sparse_dense_to_dense(A, B, C0=None):
+    """Dense result of ta.elews_mul with one sparse operand: products at the stored positions
+    (lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:1247-1284 with the "noop" reduce)."""
+    B = _f64(B)
+    C = np.zeros((A.nrows, A.ncols)) if C0 is None else _f64(C0).copy()
+    if A.format == "COO":
+        rows = _i64(A.a1crd)
+    elif A.format == "DCSR":
+        rows = np.repeat(_i64(A.a1crd)[:int(A.a1pos[1])], np.diff(_i64(A.a2pos)))
+    else:
+        rows = np.repeat(np.arange(A.nrows), np.diff(_i64(A.a2pos)))
+    cols = _i64(A.a2crd)
+    for p in range(A.nnz):          # sequential like the reference: a repeated coordinate keeps the last product
+        C[rows[p], cols[p]] = A.val[p] * B[rows[p], cols[p]]
+    return C
+
+
 def elews_csr_csr(A, B):
     L = lib()
     cpos = np.zeros(A.nrows + 1, dtype=np.int64)

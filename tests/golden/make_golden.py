@@ -64,6 +64,9 @@ CASES = {
     "ops/eltwise_mult_COOxDense_oCOO.ta": "elews_sparse_dense",
     "semiring/eltwise_monoidTimes_COOxDense_oCOO.ta": "elews_sparse_dense",
     "ops/eltwise_mult_CSRxCSR_oCSR.ta": "elews_sparse_sparse",
+    "ops/eltwise_mult_CSRxDense_oDense.ta": "elews_to_dense",
+    "ops/eltwise_mult_DCSRxDense_oDense.ta": "elews_to_dense",
+    "ops/eltwise_mult_DensexCSR_oDense.ta": "elews_to_dense",
     # sparse x sparse -> sparse
     "ops/mult_spgemm_CSRxCSR_oCSR.ta": "spgemm",
     "ops/mult_spgemm_CSRxCSR_oCSR_wMasking.ta": "spgemm_masked",

@@ -73,6 +73,12 @@ def run_case(case, mtx_dir, backend):
         vals = backend.elews_sparse_dense(A, B)
         out = oracle.SparseArrays(A.format, A.nrows, A.ncols, A.a1pos, A.a1crd, A.a2pos, A.a2crd, vals)
         return _print_sparse(out)
+    if kind == "elews_to_dense":
+        name = next(iter(read))                      # the sparse operand is A or B; the other one is dense
+        S = read[name]
+        dense = "B" if name == "A" else "A"
+        D = np.full((S.nrows, S.ncols), fills[dense])
+        return oracle.print_memref(backend.elews_sparse_dense_to_dense(S, D, np.full((S.nrows, S.ncols), fills["C"])))
     if kind == "elews_sparse_sparse":
         return _print_sparse(backend.elews_csr_csr(read["A"], read["B"]))
     if kind == "spgemm":

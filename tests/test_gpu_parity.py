@@ -408,3 +408,18 @@ def test_dense_times_sparse(fmt, tmp_path):
     _close(api.einsum("ij,jk->ik", A, B), oracle.dense_times_sparse(A, B), oracle.dense_times_sparse(np.abs(A), absB))
     assert np.array_equal(api.dense_times_sparse(x, B, semiring=api.PLUS_PAIR),
                           oracle.dense_times_sparse(x, B, semiring=oracle.PLUS_PAIR))
+
+
+@pytest.mark.parametrize("fmt", ["CSR", "DCSR", "COO"])
+def test_elews_sparse_dense_to_dense(fmt, tmp_path):
+    Am = _skewed(500, seed=41)
+    path = tmp_path / "a.mtx"
+    datasets.write_mtx(str(path), Am)
+    A = oracle.read_mtx(str(path), fmt)
+    B = datasets.dense_uniform((A.nrows, A.ncols), 4)
+    C0 = datasets.dense_uniform((A.nrows, A.ncols), 5)
+    # a product is one IEEE multiply: the results are bit-identical, untouched entries included
+    assert np.array_equal(api.elews_sparse_dense_to_dense(A, B), oracle.elews_sparse_dense_to_dense(A, B))
+    assert np.array_equal(api.elews_sparse_dense_to_dense(A, B, C0), oracle.elews_sparse_dense_to_dense(A, B, C0))
+    A32 = api.as_sparse(A).with_index_dtype(np.int32)
+    assert np.array_equal(api.elews_sparse_dense_to_dense(A32, B), oracle.elews_sparse_dense_to_dense(A, B))
