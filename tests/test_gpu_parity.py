@@ -90,6 +90,50 @@ def test_spmm_rmat_and_panel_variants():
     assert np.array_equal(Cp, np.repeat(np.diff(A.a2pos)[:, None], 128, axis=1).astype(np.float64))
 
 
+def _gappy(n=6000, seed=5):
+    """Leading, trailing and long runs of empty rows, single-entry rows and one row far longer than a block."""
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(0, 5, n)
+    lens[:70] = 0
+    lens[-130:] = 0
+    lens[2000:3400] = 0
+    lens[rng.integers(0, n, n // 2)] = 0
+    lens[1234] = 4000
+    rows = np.repeat(np.arange(n), lens)
+    cols = rng.integers(0, n, rows.shape[0])
+    m = sp.csr_matrix((rng.uniform(-1, 1, rows.shape[0]), (rows, cols)), shape=(n, n))
+    m.sum_duplicates()
+    m.sort_indices()
+    return api.as_sparse(m)
+
+
+@pytest.mark.parametrize("k", [128, 64, 96, 16, 2, 256])
+@pytest.mark.parametrize("make", [_gappy, _skewed])
+def test_spmm_entry_stream_path(make, k):
+    """The entry-stream kernel (asked for by bit 24 of the variant; the default from 64 columns and
+    65536 entries on): rows cut by block boundaries, empty rows at every position, both store modes."""
+    A = make()
+    B = datasets.dense_uniform((A.ncols, k), 3)
+    C0 = datasets.dense_uniform((A.nrows, k), 4)
+    scale = oracle.spmm(_abs(A), np.abs(B), np.abs(C0))
+    dA = dev.to_device(A)
+    dB = torch.from_numpy(B).cuda()
+    C = dev.spmm(dA, dB, variant=1 << 24)
+    _close(C.cpu().numpy(), oracle.spmm(_orc(A), B), scale)
+    C = dev.spmm(dA, dB, torch.from_numpy(C0).cuda(), accumulate=True, variant=1 << 24)
+    _close(C.cpu().numpy(), oracle.spmm(_orc(A), B, C0), scale)
+
+
+def test_spmm_entry_stream_path_dcsr(tmp_path):
+    A = _gappy(seed=6)
+    path = tmp_path / "a.mtx"
+    datasets.write_mtx(str(path), A)
+    D = oracle.read_mtx(str(path), "DCSR")
+    B = datasets.dense_uniform((D.ncols, 64), 3)
+    C = dev.spmm(dev.to_device(D), torch.from_numpy(B).cuda(), variant=1 << 24)
+    _close(C.cpu().numpy(), oracle.spmm(D, B), oracle.spmm(_abs(D), np.abs(B)))
+
+
 @pytest.mark.parametrize("fmt", ["DCSR", "COO"])
 def test_dcsr_and_coo_operands(fmt, tmp_path):
     A = _skewed(500, seed=9)
