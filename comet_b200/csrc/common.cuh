@@ -50,6 +50,7 @@ enum Slot {
     SLOT_BITMAP,         // per-CTA global bitmaps when a row of columns exceeds shared memory
     SLOT_POS,            // COO -> row pointer adapter
     SLOT_MISC,
+    SLOT_TEAMS,          // team item list of the SpGEMM numeric pass
     SLOT_H2D_0, SLOT_H2D_1, SLOT_H2D_2, SLOT_H2D_3, SLOT_H2D_4, SLOT_H2D_5,
     SLOT_H2D_6, SLOT_H2D_7, SLOT_H2D_8, SLOT_H2D_9, SLOT_H2D_10, SLOT_H2D_11,
     SLOT_COUNT

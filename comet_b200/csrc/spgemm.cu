@@ -314,25 +314,117 @@ __device__ __forceinline__ unsigned block_sum_u32(unsigned v, unsigned *s_warp)
     return t;
 }
 
+// Rows of B longer than this are walked by the whole CTA instead of one warp: in a power-law
+// product a few such rows hold most of the work of an output row, and one warp working alone while
+// fifteen wait at the next barrier was the largest stall of both passes.
+static const int64_t LONG_B_ROW = 1024;
+
+static const int LONG_LIST = 1024;          // long rows of B remembered per pass over a row of A
+
+// Calls f(q, p) for every product of row r of A with B in this CTA's share: q runs over the entries
+// of row acrd[p] of B.  A team of `team` CTAs deals the entries p of the A row out over its warps.
+// Short rows of B are walked by one warp; long ones are remembered in s_long and then walked by the
+// whole CTA.  s_ctl: [0] entries in s_long, [1] set when the list was too small (then the share is
+// scanned again for long rows).  All threads of the CTA must call this.
+template <typename F>
+__device__ __forceinline__ void for_each_product(int64_t r, unsigned part, unsigned team,
+                                                 const int64_t *__restrict__ apos,
+                                                 const int64_t *__restrict__ acrd,
+                                                 const double *__restrict__ aval,
+                                                 const int64_t *__restrict__ bpos, int *s_long,
+                                                 unsigned *s_ctl, F f)
+{
+    constexpr int NW = BM_THREADS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t as = apos[r], ae = apos[r + 1];
+    if (threadIdx.x == 0) { s_ctl[0] = 0; s_ctl[1] = 0; }
+    __syncthreads();
+    // the row of B of the next entry is looked up while the current one is walked
+    const int64_t stride = (int64_t)team * NW;
+    int64_t p = as + (int64_t)part * NW + warp;
+    int64_t s = 0, e = 0;
+    double av = 0.0;
+    if (p < ae) {
+        const int64_t k = acrd[p];
+        s = bpos[k];
+        e = bpos[k + 1];
+        if (aval) av = aval[p];
+    }
+    while (p < ae) {
+        const int64_t pn = p + stride;
+        int64_t sn = 0, en = 0;
+        double avn = 0.0;
+        if (pn < ae) {
+            const int64_t kn = acrd[pn];
+            sn = bpos[kn];
+            en = bpos[kn + 1];
+            if (aval) avn = aval[pn];
+        }
+        if (e - s > LONG_B_ROW) {
+            if (lane == 0) {
+                const unsigned at = atomicAdd(&s_ctl[0], 1u);
+                if (at < (unsigned)LONG_LIST) s_long[at] = (int)(p - as);
+                else s_ctl[1] = 1;
+            }
+        } else {
+            for (int64_t q = s + lane; q < e; q += 32) f(q, av);
+        }
+        p = pn; s = sn; e = en; av = avn;
+    }
+    __syncthreads();
+    if (!s_ctl[1]) {
+        const unsigned n = s_ctl[0];
+        for (unsigned i = 0; i < n; i++) {
+            const int64_t pl = as + s_long[i];
+            const int64_t k = acrd[pl];
+            const int64_t el = bpos[k + 1];
+            const double avl = aval ? aval[pl] : 0.0;
+            for (int64_t q = bpos[k] + threadIdx.x; q < el; q += BM_THREADS) f(q, avl);
+        }
+    } else {
+        for (int64_t p0 = as + (int64_t)part * NW; p0 < ae; p0 += stride)
+            for (int64_t pl = p0; pl < p0 + NW && pl < ae; pl++) {
+                const int64_t k = acrd[pl];
+                const int64_t sl = bpos[k], el = bpos[k + 1];
+                if (el - sl <= LONG_B_ROW) continue;
+                const double avl = aval ? aval[pl] : 0.0;
+                for (int64_t q = sl + threadIdx.x; q < el; q += BM_THREADS) f(q, avl);
+            }
+    }
+}
+
 // marks the columns of row r's products in bm (bm cleared by the caller)
 __device__ __forceinline__ void mark_products(uint32_t *bm, int64_t r, const int64_t *__restrict__ apos,
                                               const int64_t *__restrict__ acrd,
                                               const int64_t *__restrict__ bpos,
                                               const int32_t *__restrict__ bcrd,
                                               const int64_t *__restrict__ mpos,
-                                              const int64_t *__restrict__ mcrd)
+                                              const int64_t *__restrict__ mcrd, int *s_long, unsigned *s_ctl)
 {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int64_t ms = 0, me = 0;
     if (mpos) { ms = mpos[r]; me = mpos[r + 1]; }
-    for (int64_t p = apos[r] + warp; p < apos[r + 1]; p += BM_THREADS / 32) {
-        const int64_t k = acrd[p];
-        for (int64_t q = bpos[k] + lane; q < bpos[k + 1]; q += 32) {
-            int32_t j = bcrd[q];
-            if (mpos && !in_mask(mcrd, ms, me, j)) continue;
-            atomicOr(&bm[j >> 5], 1u << (j & 31));
-        }
+    for_each_product(r, 0u, 1u, apos, acrd, nullptr, bpos, s_long, s_ctl, [&](int64_t q, double) {
+        int32_t j = bcrd[q];
+        if (mpos && !in_mask(mcrd, ms, me, j)) return;
+        atomicOr(&bm[j >> 5], 1u << (j & 31));
+    });
+}
+
+// exclusive prefix sum of one value per thread over the CTA (s_warp: one slot per warp)
+__device__ __forceinline__ unsigned block_excl_scan_u32(unsigned v, unsigned *s_warp)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned incl = v;
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
     }
+    __syncthreads();                    // s_warp may still be read by the previous use
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    unsigned before = 0;
+    for (int w = 0; w < warp; w++) before += s_warp[w];
+    return before + incl - v;
 }
 
 template <bool SMEM>
@@ -346,12 +438,14 @@ bitmap_symbolic_kernel(unsigned nlist, const int32_t *__restrict__ list, int wor
 {
     extern __shared__ uint32_t s_dyn[];
     __shared__ unsigned s_warp[BM_THREADS / 32];
+    __shared__ int s_long[LONG_LIST];
+    __shared__ unsigned s_ctl[2];
     uint32_t *bm = SMEM ? s_dyn : gbm + (size_t)blockIdx.x * words;
     for (unsigned it = blockIdx.x; it < nlist; it += gridDim.x) {
         const int64_t r = list[it];
         for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = 0;
         __syncthreads();
-        mark_products(bm, r, apos, acrd, bpos, bcrd, mpos, mcrd);
+        mark_products(bm, r, apos, acrd, bpos, bcrd, mpos, mcrd, s_long, s_ctl);
         __syncthreads();
         unsigned c = 0;
         uint32_t *keep = bm_store ? bm_store + (size_t)it * words : nullptr;
@@ -366,8 +460,85 @@ bitmap_symbolic_kernel(unsigned nlist, const int32_t *__restrict__ list, int wor
     }
 }
 
-template <bool SMEM>
-__global__ void __launch_bounds__(BM_THREADS)
+// --------------------------------------------------------------------------
+// Teams for the numeric pass of bin-2 rows.
+//
+// f64 atomics run at ~200 G/s while their targets stay in L2 and at 20-80 G/s once the rows being
+// accumulated no longer fit (measured on this part with a stand-alone probe).  With one CTA per row
+// the rows in flight of a power-law product hold far more than L2, so a row whose output is large
+// is given to a team of T CTAs instead: they split the entries of the A row, add into the same
+// output row, and T is chosen so that (CTAs in flight / T) rows of that size fit the budget.
+// Teams are laid out contiguously in an item list and CTAs draw items in order, so the members of a
+// team run at about the same time.  The values of team rows are cleared by a separate launch
+// (a member must not start adding before another has cleared); single-CTA rows clear their own.
+// --------------------------------------------------------------------------
+struct TeamHeader {
+    unsigned nitems;
+    unsigned next;
+    unsigned overflow;
+    unsigned pad;
+};
+static const unsigned TEAM_MAX = 64;
+
+__device__ __forceinline__ uint64_t team_pack(unsigned it, unsigned part, unsigned t)
+{
+    return (uint64_t)it | ((uint64_t)part << 32) | ((uint64_t)t << 48);
+}
+
+__global__ void __launch_bounds__(256)
+team_items_kernel(unsigned nlist, const int32_t *__restrict__ list, const int64_t *__restrict__ cpos,
+                  double ctas_per_budget_entry, TeamHeader *th, uint64_t *items, unsigned cap)
+{
+    // consecutive list entries in consecutive slots (one warp-wide scan per 32 rows keeps the list ordered)
+    const unsigned it = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    unsigned t = 0;
+    if (it < nlist) {
+        const int64_t r = list[it];
+        const double want = (double)(cpos[r + 1] - cpos[r]) * ctas_per_budget_entry;
+        t = want <= 1.0 ? 1u : (want >= (double)TEAM_MAX ? TEAM_MAX : (unsigned)ceil(want));
+    }
+    unsigned incl = t;
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    unsigned base = 0;
+    if (lane == 31) base = atomicAdd(&th->nitems, incl);
+    base = __shfl_sync(0xffffffffu, base, 31) + incl - t;
+    if (t) {
+        if (base + t <= cap) {
+            for (unsigned i = 0; i < t; i++) items[base + i] = team_pack(it, i, t);
+        } else {
+            th->overflow = 1;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+team_clear_kernel(const TeamHeader *th, const uint64_t *__restrict__ items, unsigned cap,
+                  const int32_t *__restrict__ list, const int64_t *__restrict__ cpos, int semi,
+                  double *__restrict__ cval)
+{
+    unsigned n = th->nitems;
+    if (n > cap) n = 0;
+    const double ident = sr_identity(semi);
+    for (unsigned i = blockIdx.x; i < n; i += gridDim.x) {
+        const uint64_t v = items[i];
+        const unsigned t = (unsigned)(v >> 48), part = (unsigned)(v >> 32) & 0xffffu;
+        if (t <= 1) continue;
+        const int64_t r = list[(unsigned)v];
+        const int64_t base = cpos[r], n_out = cpos[r + 1] - base;
+        const int64_t per = (n_out + t - 1) / t;
+        const int64_t s = base + (int64_t)part * per;
+        int64_t e = s + per;
+        if (e > base + n_out) e = base + n_out;
+        for (int64_t q = s + threadIdx.x; q < e; q += blockDim.x) cval[q] = ident;
+    }
+}
+
+template <bool SMEM, bool PLUS_TIMES>
+__global__ void __launch_bounds__(BM_THREADS, SMEM ? 3 : 1)
 bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int words,
                       uint32_t *__restrict__ gbm, const int64_t *__restrict__ apos,
                       const int64_t *__restrict__ acrd, const double *__restrict__ aval,
@@ -375,16 +546,33 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
                       const double *__restrict__ bval, const int64_t *__restrict__ mpos,
                       const int64_t *__restrict__ mcrd, int semi,
                       const uint32_t *__restrict__ bm_store, const int64_t *__restrict__ cpos,
-                      int64_t *__restrict__ ccrd, double *__restrict__ cval)
+                      int64_t *__restrict__ ccrd, double *__restrict__ cval, TeamHeader *th,
+                      const uint64_t *__restrict__ items)
 {
     extern __shared__ uint32_t s_dyn[];
-    __shared__ unsigned s_warp[BM_THREADS / 32];
-    __shared__ unsigned s_scan[BM_THREADS];
+    __shared__ unsigned s_item;
+    __shared__ unsigned s_scan[BM_THREADS / 32];
+    __shared__ int s_long[LONG_LIST];
+    __shared__ unsigned s_ctl[2];
     uint32_t *bm = SMEM ? s_dyn : gbm + (size_t)blockIdx.x * 2 * words;
     uint32_t *pre = bm + words;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per = (words + BM_THREADS - 1) / BM_THREADS;   // words per thread, contiguous
-    for (unsigned it = blockIdx.x; it < nlist; it += gridDim.x) {
+    for (unsigned iter = blockIdx.x;; iter += gridDim.x) {
+        // one row per CTA, or (with an item list) the next member of a team
+        unsigned it = iter, part = 0, team = 1;
+        if (th) {
+            if (threadIdx.x == 0) s_item = atomicAdd(&th->next, 1u);
+            __syncthreads();
+            const unsigned idx = s_item;
+            if (idx >= th->nitems) break;
+            const uint64_t v = items[idx];
+            it = (unsigned)v;
+            part = (unsigned)(v >> 32) & 0xffffu;
+            team = (unsigned)(v >> 48);
+        } else if (iter >= nlist) {
+            break;
+        }
         const int64_t r = list[it];
         if (bm_store) {
             const uint32_t *keep = bm_store + (size_t)it * words;
@@ -393,53 +581,48 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
         } else {
             for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = 0;
             __syncthreads();
-            mark_products(bm, r, apos, acrd, bpos, bcrd, mpos, mcrd);
+            mark_products(bm, r, apos, acrd, bpos, bcrd, mpos, mcrd, s_long, s_ctl);
             __syncthreads();
         }
         // exclusive prefix popcount per word
         const int w0 = threadIdx.x * per, w1 = min(w0 + per, words);
         unsigned mine = 0;
         for (int w = w0; w < w1; w++) mine += __popc(bm[w]);
-        s_scan[threadIdx.x] = mine;
-        __syncthreads();
-        // Hillis-Steele inclusive scan over BM_THREADS partial sums
-        for (int o = 1; o < BM_THREADS; o <<= 1) {
-            unsigned t = threadIdx.x >= o ? s_scan[threadIdx.x - o] : 0;
-            __syncthreads();
-            s_scan[threadIdx.x] += t;
-            __syncthreads();
-        }
-        unsigned run = s_scan[threadIdx.x] - mine;
+        unsigned run = block_excl_scan_u32(mine, s_scan);
         const int64_t base = cpos[r];
         const int64_t rown = cpos[r + 1] - base;
+        const bool my_crd = (threadIdx.x % team) == part;     // the members share the writing of crd
         for (int w = w0; w < w1; w++) {
             uint32_t v = bm[w];
             pre[w] = run;
-            while (v) {
-                int b = __ffs(v) - 1;
-                v &= v - 1;
-                ccrd[base + run] = (int64_t)w * 32 + b;
-                run++;
+            if (my_crd) {
+                while (v) {
+                    int b = __ffs(v) - 1;
+                    v &= v - 1;
+                    __stcs((long long *)ccrd + base + run, (long long)w * 32 + b);   // written once, not read here again
+                    run++;
+                }
+            } else {
+                run += __popc(v);
             }
         }
-        for (int64_t t = threadIdx.x; t < rown; t += BM_THREADS) cval[base + t] = sr_identity(semi);
+        if (team == 1)
+            for (int64_t t = threadIdx.x; t < rown; t += BM_THREADS) cval[base + t] = sr_identity(semi);
         __syncthreads();
         // accumulate every product at the rank of its column
-        for (int64_t p = apos[r] + warp; p < apos[r + 1]; p += BM_THREADS / 32) {
-            const int64_t k = acrd[p];
-            const double av = aval[p];
-            for (int64_t q = bpos[k] + lane; q < bpos[k + 1]; q += 32) {
-                int32_t j = bcrd[q];
-                uint32_t word = bm[j >> 5];
-                uint32_t bit = 1u << (j & 31);
-                if (!(word & bit)) continue;   // filtered out by the mask
-                unsigned rank = pre[j >> 5] + __popc(word & (bit - 1u));
-                sr_fold(semi, &cval[base + rank], sr_combine(semi, av, bval[q]));
-            }
-        }
+        double *crow = cval + base;
+        for_each_product(r, part, team, apos, acrd, aval, bpos, s_long, s_ctl, [&](int64_t q, double av) {
+            int32_t j = bcrd[q];
+            uint32_t word = bm[j >> 5];
+            uint32_t bit = 1u << (j & 31);
+            if (!(word & bit)) return;          // filtered out by the mask
+            unsigned rank = pre[j >> 5] + __popc(word & (bit - 1u));
+            if (PLUS_TIMES) atomicAdd(crow + rank, av * bval[q]);
+            else sr_fold(semi, crow + rank, sr_combine(semi, av, bval[q]));
+        });
         __syncthreads();
     }
-    (void)s_warp; (void)mpos; (void)mcrd;
+    (void)mpos; (void)mcrd;
 }
 
 // --------------------------------------------------------------------------
@@ -633,20 +816,52 @@ int sparse_out_numeric(int64_t handle, int64_t *ccrd, double *cval, int keep, cu
         if (!rc && p->n2) {
             size_t smem = (size_t)p->words * sizeof(uint32_t) * 2;
             if (smem <= BM_SMEM_LIMIT) {
-                int grid = bitmap_grid(p->n2, smem);
-                cudaFuncSetAttribute(bitmap_numeric_kernel<true>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                bitmap_numeric_kernel<true><<<grid, BM_THREADS, smem, st>>>(
-                    p->n2, p->list2, p->words, nullptr, p->apos, p->acrd, p->aval, p->bpos, p->bcrd32,
-                    p->bval, p->mpos, p->mcrd, p->semi, p->bm_store, p->cpos, ccrd, cval);
+                // full occupancy grid even for few rows: teams give every CTA work
+                int grid = bitmap_grid(0xffffffffu, smem);
+                // team size of a row = its output entries * 8 bytes * CTAs in flight / budget
+                static double budget_mb = -1.0;
+                if (budget_mb < 0.0) {
+                    const char *e = getenv("COMET_B200_SPGEMM_TEAM_MB");
+                    budget_mb = e ? atof(e) : 60.0;
+                    if (budget_mb < 1.0) budget_mb = 1.0;
+                }
+                const double per_entry = 8.0 * grid / (budget_mb * 1048576.0);
+                const size_t cap = (size_t)p->n2 + (size_t)((double)p->nnz_c * per_entry) + 64;
+                void *tm = nullptr;
+                rc = cap > 0xfffffff0u ? fail("spgemm numeric: too many team items")
+                                       : scratch(SLOT_TEAMS, sizeof(TeamHeader) + cap * sizeof(uint64_t), &tm);
+                TeamHeader *th = (TeamHeader *)tm;
+                uint64_t *items = (uint64_t *)((char *)tm + sizeof(TeamHeader));
+                if (!rc && cudaMemsetAsync(th, 0, sizeof(TeamHeader), st) != cudaSuccess)
+                    rc = fail("spgemm numeric: clearing the team header failed");
+                if (!rc) {
+                    team_items_kernel<<<(unsigned)ceil_div(p->n2, 256), 256, 0, st>>>(
+                        p->n2, p->list2, p->cpos, per_entry, th, items, (unsigned)cap);
+                    team_clear_kernel<<<(unsigned)sm_count() * 8, 256, 0, st>>>(th, items, (unsigned)cap, p->list2,
+                                                                                p->cpos, p->semi, cval);
+                    if (p->semi == COMET_B200_PLUS_TIMES) {
+                        cudaFuncSetAttribute(bitmap_numeric_kernel<true, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                        bitmap_numeric_kernel<true, true><<<grid, BM_THREADS, smem, st>>>(
+                            p->n2, p->list2, p->words, nullptr, p->apos, p->acrd, p->aval, p->bpos, p->bcrd32,
+                            p->bval, p->mpos, p->mcrd, p->semi, p->bm_store, p->cpos, ccrd, cval, th, items);
+                    } else {
+                        cudaFuncSetAttribute(bitmap_numeric_kernel<true, false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                        bitmap_numeric_kernel<true, false><<<grid, BM_THREADS, smem, st>>>(
+                            p->n2, p->list2, p->words, nullptr, p->apos, p->acrd, p->aval, p->bpos, p->bcrd32,
+                            p->bval, p->mpos, p->mcrd, p->semi, p->bm_store, p->cpos, ccrd, cval, th, items);
+                    }
+                }
             } else {
                 int grid = bitmap_grid(p->n2, 0);
                 void *gbm = nullptr;
                 rc = scratch(SLOT_BITMAP, (size_t)grid * smem, &gbm);
                 if (!rc)
-                    bitmap_numeric_kernel<false><<<grid, BM_THREADS, 0, st>>>(
+                    bitmap_numeric_kernel<false, false><<<grid, BM_THREADS, 0, st>>>(
                         p->n2, p->list2, p->words, (uint32_t *)gbm, p->apos, p->acrd, p->aval, p->bpos,
-                        p->bcrd32, p->bval, p->mpos, p->mcrd, p->semi, p->bm_store, p->cpos, ccrd, cval);
+                        p->bcrd32, p->bval, p->mpos, p->mcrd, p->semi, p->bm_store, p->cpos, ccrd, cval, nullptr,
+                        nullptr);
             }
             if (!rc && cudaGetLastError() != cudaSuccess) rc = fail("spgemm numeric (bitmap) launch failed");
         }
