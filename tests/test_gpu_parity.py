@@ -215,6 +215,32 @@ def test_spgemm_rectangular_empty_and_long_rows():
     assert got.nnz == 0 and np.all(got.a2pos == 0)
 
 
+@pytest.mark.parametrize("semiring", [api.PLUS_TIMES, api.MIN_PLUS])
+def test_spgemm_teams_and_long_rows_of_b(monkeypatch, semiring):
+    """Rows whose output is large are accumulated by a team of CTAs (forced here by a tiny budget), and
+    rows of B above 1024 entries are walked by the whole CTA: row 1500 of A names 1200 such rows, more
+    than the per-CTA list of long rows holds, so the rescan path runs too."""
+    rng = np.random.default_rng(3)
+    n, nlong, width = 4096, 1200, 1030
+    rows, cols = [], []
+    for i in range(nlong):                               # long rows, pointing at short ones
+        rows.append(np.full(width, i)); cols.append(nlong + np.sort(rng.choice(n - nlong, width, replace=False)))
+    for i in range(nlong, n):
+        c = np.arange(nlong) if i == 1500 else np.sort(rng.choice(n, 3, replace=False))
+        rows.append(np.full(c.shape[0], i)); cols.append(c)
+    rows, cols = np.concatenate(rows), np.concatenate(cols)
+    m = sp.csr_matrix((rng.uniform(-1, 1, rows.shape[0]), (rows, cols)), shape=(n, n))
+    m.sort_indices()
+    A = api.as_sparse(m)
+    for budget in ("0.01", "60"):
+        monkeypatch.setenv("COMET_B200_SPGEMM_TEAM_MB", budget)
+        _check_spgemm(A, A, semiring=semiring)
+    R = datasets.rmat_csr(12, 16, seed=4)
+    monkeypatch.setenv("COMET_B200_SPGEMM_TEAM_MB", "0.01")
+    _check_spgemm(R, R, semiring=semiring)
+    _check_spgemm(R, R, datasets.rmat_csr(12, 32, seed=5), semiring)
+
+
 def test_spgemm_many_columns_uses_global_bitmaps():
     rng = np.random.default_rng(1)
     n = 1_200_000                                    # bitmap + ranks no longer fit shared memory
