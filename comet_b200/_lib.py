@@ -35,6 +35,7 @@ SIGNATURES = {
     "comet_b200_spgemm_symbolic_f64_i64": (c_int64, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF * 2),
     "comet_b200_spgemm_numeric_f64_i64": (None, [c_int64] + _MEMREF * 2),
     "comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64": (c_int64, _SPARSE * 2 + _MEMREF * 2),
+    "comet_b200_transpose_2D_f64_i64": (None, ([c_int32] * 4 + [c_int64, c_void_p] * 9) * 2 + _MEMREF),
     "comet_b200_handle_destroy": (None, [c_int64]),
     "comet_b200_masked_spgemm_count_f64_i64": (None, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF),
     "comet_b200_last_error": (ctypes.c_char_p, []),
@@ -52,6 +53,9 @@ SIGNATURES = {
     "comet_b200_dev_sddmm_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 4 + [c_int64, c_void_p, c_int64,
                                                c_void_p, c_void_p]),
     "comet_b200_dev_transpose_f64": (c_int32, [c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "comet_b200_dev_sort_coo_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 7),
+    "comet_b200_dev_coo_to_csr_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 7),
+    "comet_b200_dev_csr_transpose_f64_i64": (c_int32, [c_int64] * 3 + [c_void_p] * 7),
     "comet_b200_dev_elews_mul_sparse_dense_f64_i64": (c_int32, [c_int64, c_int64] + [c_void_p] * 5 +
                                                       [c_int64, c_void_p, c_void_p]),
     "comet_b200_dev_elews_mul_sparse_dense_to_dense_f64_i64": (c_int32, [c_int64, c_int64] + [c_void_p] * 6 +

@@ -322,6 +322,61 @@ def triangle_count(L):
     return masked_pair_count(L, L, L)
 
 
+def transpose(A):
+    """Transpose of a CSR or COO matrix in the same format, through the entry point that stands in
+    for the reference runtime's transpose_2D_f64_i64 (lib/ExecutionEngine/TransposeUtils.cpp:1439)."""
+    A = as_sparse(A)
+    if A.format not in ("CSR", "COO"):
+        raise ValueError("transpose: CSR and COO are handled")
+    lib = _lib.load()
+    dt = A.index_dtype if A.index_dtype == np.int32 else np.dtype(np.int64)
+    A = A.with_index_dtype(dt)
+    fn = getattr(lib, "comet_b200_transpose_2D_f64_%s" % ("i32" if dt == np.int32 else "i64"))
+    pk = _Packer()
+    nnz = A.nnz
+    if A.format == "CSR":
+        b1pos, b1crd = np.zeros(1, dtype=dt), np.zeros(1, dtype=dt)
+        b2pos = np.zeros(A.ncols + 1, dtype=dt)
+    else:
+        b1pos, b1crd = np.zeros(2, dtype=dt), np.zeros(nnz, dtype=dt)
+        b2pos = np.zeros(1, dtype=dt)
+    b2crd, bval = np.zeros(nnz, dtype=dt), np.zeros(nnz)
+    sizes = np.array([A.nrows, A.ncols] + [0] * 9, dtype=dt)
+    empty = np.zeros(0, dtype=dt)
+    f1, f2 = _FMT[A.format]
+
+    def block(a1pos, a1crd, a2pos, a2crd, val):
+        return ([f1, -1, f2, -1] + pk.m1(a1pos) + pk.m1(a1crd) + pk.m1(empty) + pk.m1(empty) + pk.m1(a2pos) +
+                pk.m1(a2crd) + pk.m1(empty) + pk.m1(empty) + pk.m1(val))
+
+    fn(*block(A.a1pos, A.a1crd, A.a2pos, A.a2crd, A.val), *block(b1pos, b1crd, b2pos, b2crd, bval), *pk.m1(sizes))
+    _lib.check()
+    return SparseTensor(A.format, int(sizes[0]), int(sizes[1]), b1pos, b1crd, b2pos, b2crd, bval)
+
+
+def from_coordinates(rows, cols, vals, shape):
+    """CSR from coordinate entries in any order, sorted on the device the way the reference reader sorts
+    them on the host (by row, then column; entries with equal coordinates stay in input order and are
+    kept, lib/ExecutionEngine/SparseUtils.cpp:360-533)."""
+    import torch
+    lib = _lib.load()
+    nrows, ncols = int(shape[0]), int(shape[1])
+    r = torch.from_numpy(_i64(rows)).cuda()
+    c = torch.from_numpy(_i64(cols)).cuda()
+    v = torch.from_numpy(_f64(vals)).cuda()
+    nnz = int(r.shape[0])
+    pos = torch.empty(nrows + 1, dtype=torch.int64, device="cuda")
+    crd = torch.empty(nnz, dtype=torch.int64, device="cuda")
+    val = torch.empty(nnz, dtype=torch.float64, device="cuda")
+    st = lib.comet_b200_dev_coo_to_csr_f64_i64(nrows, ncols, nnz, r.data_ptr(), c.data_ptr(), v.data_ptr(),
+                                               pos.data_ptr(), crd.data_ptr(), val.data_ptr(),
+                                               torch.cuda.current_stream().cuda_stream)
+    _lib.check(st)
+    torch.cuda.synchronize()
+    return SparseTensor("CSR", nrows, ncols, np.array([nrows], dtype=np.int64), np.array([-1], dtype=np.int64),
+                        pos.cpu().numpy(), crd.cpu().numpy(), val.cpu().numpy())
+
+
 def reduce_sum(vals):
     """ta.reduce over stored values.  Not part of the device path: the values are
     host memrefs after every call, and COMET's generated loop sums them there

@@ -555,6 +555,102 @@ static void elews_to_dense_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank,
     finish(st);
 }
 
+// n int64 indices on the device -> the caller's array of isz-byte integers
+static int download_idx(DevBag &bag, const int64_t *dev, char *host, int64_t n, int isz, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    if (isz == 8) {
+        CB_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * 8, cudaMemcpyDeviceToHost, st));
+        return 0;
+    }
+    int32_t *d32 = nullptr;
+    CB_TRY(bag.alloc((void **)&d32, (size_t)n * 4));
+    CB_TRY(narrow_any_i64_to_i32(dev, d32, n, st));
+    CB_CUDA(cudaMemcpyAsync(host, d32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    return 0;
+}
+
+// B = transpose(A) for CSR -> CSR and COO -> COO, the two pairs transpose_2D handles
+// (lib/ExecutionEngine/TransposeUtils.cpp:625-812).  The caller allocated B's arrays; like the
+// reference this fills them, writes the placeholders (B1pos = {rows of B}, B1crd = {-1} for CSR;
+// B1pos = {0, nnz} for COO) and swaps the two dimension sizes in `sizes`.
+static void transpose_impl(int isz, int32_t A1format, int32_t A2format, int64_t A1pos_rank, void *A1pos_ptr,
+                           int64_t A1crd_rank, void *A1crd_ptr, int64_t A2pos_rank, void *A2pos_ptr,
+                           int64_t A2crd_rank, void *A2crd_ptr, int64_t Aval_rank, void *Aval_ptr, int32_t B1format,
+                           int32_t B2format, int64_t B1pos_rank, void *B1pos_ptr, int64_t B1crd_rank, void *B1crd_ptr,
+                           int64_t B2pos_rank, void *B2pos_ptr, int64_t B2crd_rank, void *B2crd_ptr,
+                           int64_t Bval_rank, void *Bval_ptr, int64_t sizes_rank, void *sizes_ptr)
+{
+    clear_error();
+    Arr a1pos, a1crd, a2pos, a2crd, aval, b1pos, b1crd, b2pos, b2crd, bval, sizes;
+    if (get1d("transpose: A1pos", A1pos_rank, A1pos_ptr, isz, &a1pos) || get1d("transpose: A1crd", A1crd_rank, A1crd_ptr, isz, &a1crd) ||
+        get1d("transpose: A2pos", A2pos_rank, A2pos_ptr, isz, &a2pos) || get1d("transpose: A2crd", A2crd_rank, A2crd_ptr, isz, &a2crd) ||
+        get1d("transpose: Aval", Aval_rank, Aval_ptr, 8, &aval) || get1d("transpose: B1pos", B1pos_rank, B1pos_ptr, isz, &b1pos) ||
+        get1d("transpose: B1crd", B1crd_rank, B1crd_ptr, isz, &b1crd) || get1d("transpose: B2pos", B2pos_rank, B2pos_ptr, isz, &b2pos) ||
+        get1d("transpose: B2crd", B2crd_rank, B2crd_ptr, isz, &b2crd) || get1d("transpose: Bval", Bval_rank, Bval_ptr, 8, &bval) ||
+        get1d("transpose: sizes", sizes_rank, sizes_ptr, isz, &sizes))
+        return;
+    if (!sizes.data || sizes.n < 2) { fail("transpose: sizes must hold {rows, cols}"); return; }
+    const int64_t nrows = idx_get((char *)sizes.data, 0, isz), ncols = idx_get((char *)sizes.data, 1, isz);
+    if (nrows < 0 || ncols < 0) { fail("transpose: negative dimension"); return; }
+    const bool a_csr = A1format == COMET_B200_FMT_DENSE && A2format == COMET_B200_FMT_CU;
+    const bool a_coo = A1format == COMET_B200_FMT_CN && A2format == COMET_B200_FMT_S;
+    const bool b_csr = B1format == COMET_B200_FMT_DENSE && B2format == COMET_B200_FMT_CU;
+    const bool b_coo = B1format == COMET_B200_FMT_CN && B2format == COMET_B200_FMT_S;
+    if (!((a_csr && b_csr) || (a_coo && b_coo))) {
+        fail("transpose: only CSR -> CSR and COO -> COO are handled (as in the reference runtime)");
+        return;
+    }
+    int64_t nnz = 0;
+    if (a_csr) {
+        if (a2pos.n < nrows + 1) { fail("transpose: A2pos shorter than rows+1"); return; }
+        int64_t prev = 0;
+        for (int64_t i = 0; i <= nrows; i++) {
+            const int64_t cur = idx_get((char *)a2pos.data, i, isz);
+            if ((i == 0 && cur != 0) || cur < prev) { fail("transpose: A2pos is not a row pointer"); return; }
+            prev = cur;
+        }
+        nnz = prev;
+        if (b2pos.n < ncols + 1) { fail("transpose: B2pos shorter than cols+1"); return; }
+    } else {
+        if (a1pos.n < 2) { fail("transpose: COO A1pos must hold {0, nnz}"); return; }
+        nnz = idx_get((char *)a1pos.data, 1, isz);
+        if (nnz < 0 || a1crd.n < nnz || b1crd.n < nnz || b1pos.n < 2) { fail("transpose: COO arrays shorter than nnz"); return; }
+    }
+    if (a2crd.n < nnz || aval.n < nnz || b2crd.n < nnz || bval.n < nnz) { fail("transpose: crd/val arrays shorter than nnz"); return; }
+    cudaStream_t st;
+    if (need_stream(&st)) return;
+    DevBag bag(st);
+    int64_t *dcrd = nullptr, *dmaj = nullptr, *omaj = nullptr, *ocrd = nullptr;
+    double *dval = nullptr, *oval = nullptr;
+    if (bag.upload_idx(&dcrd, a2crd.data, nnz, isz) || bag.upload((void **)&dval, aval.data, (size_t)nnz * 8) ||
+        bag.alloc((void **)&ocrd, (size_t)nnz * 8) || bag.alloc((void **)&oval, (size_t)nnz * 8))
+        return;
+    if (a_csr) {
+        int64_t *dpos = nullptr;
+        if (bag.upload_idx(&dpos, a2pos.data, nrows + 1, isz) || bag.alloc((void **)&omaj, (size_t)(ncols + 1) * 8)) return;
+        if (comet_b200_dev_csr_transpose_f64_i64(nrows, ncols, nnz, dpos, dcrd, dval, omaj, ocrd, oval, st)) return;
+        if (download_idx(bag, omaj, (char *)b2pos.data, ncols + 1, isz, st)) return;
+        if (b1pos.data && b1pos.n >= 1) idx_set((char *)b1pos.data, 0, isz, ncols);
+        if (b1crd.data && b1crd.n >= 1) idx_set((char *)b1crd.data, 0, isz, -1);
+    } else {
+        if (bag.upload_idx(&dmaj, a1crd.data, nnz, isz) || bag.alloc((void **)&omaj, (size_t)nnz * 8)) return;
+        // sorted by (column, row) of the input: the transposed matrix in the reader's order
+        if (comet_b200_dev_sort_coo_f64_i64(nnz, ncols, nrows, dcrd, dmaj, dval, omaj, ocrd, oval, st)) return;
+        if (download_idx(bag, omaj, (char *)b1crd.data, nnz, isz, st)) return;
+        idx_set((char *)b1pos.data, 0, isz, 0);
+        idx_set((char *)b1pos.data, 1, isz, nnz);
+    }
+    if (download_idx(bag, ocrd, (char *)b2crd.data, nnz, isz, st)) return;
+    if (nnz && cudaMemcpyAsync(bval.data, oval, (size_t)nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+        fail("transpose: copy of the values failed");
+        return;
+    }
+    if (finish(st)) return;
+    idx_set((char *)sizes.data, 0, isz, ncols);
+    idx_set((char *)sizes.data, 1, isz, nrows);
+}
+
 // Dense x sparse: A is a rank-1 (vector) or rank-2 row-major memref, C has the same rank.
 static void dense_sparse_impl(int isz, int64_t A_rank, void *A_ptr, COMET_B200_SPARSE2D(B), int64_t C_rank,
                               void *C_ptr, int32_t semiring, int32_t accumulate)
@@ -837,3 +933,27 @@ BOTH_WIDTHS(void, masked_spgemm_count, masked_count_impl,
             FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, out_rank, out_ptr)
 
 }  // extern "C"
+
+#define TRANSPOSE_ARGS                                                                                               \
+    int32_t A1format, int32_t A1tile_format, int32_t A2format, int32_t A2tile_format, int64_t A1pos_rank,            \
+        void *A1pos_ptr, int64_t A1crd_rank, void *A1crd_ptr, int64_t A1tile_pos_rank, void *A1tile_pos_ptr,         \
+        int64_t A1tile_crd_rank, void *A1tile_crd_ptr, int64_t A2pos_rank, void *A2pos_ptr, int64_t A2crd_rank,      \
+        void *A2crd_ptr, int64_t A2tile_pos_rank, void *A2tile_pos_ptr, int64_t A2tile_crd_rank,                     \
+        void *A2tile_crd_ptr, int64_t Aval_rank, void *Aval_ptr, int32_t B1format, int32_t B1tile_format,            \
+        int32_t B2format, int32_t B2tile_format, int64_t B1pos_rank, void *B1pos_ptr, int64_t B1crd_rank,            \
+        void *B1crd_ptr, int64_t B1tile_pos_rank, void *B1tile_pos_ptr, int64_t B1tile_crd_rank,                     \
+        void *B1tile_crd_ptr, int64_t B2pos_rank, void *B2pos_ptr, int64_t B2crd_rank, void *B2crd_ptr,              \
+        int64_t B2tile_pos_rank, void *B2tile_pos_ptr, int64_t B2tile_crd_rank, void *B2tile_crd_ptr,                \
+        int64_t Bval_rank, void *Bval_ptr, int64_t sizes_rank, void *sizes_ptr
+#define TRANSPOSE_BODY(ISZ)                                                                                          \
+    (void)A1tile_format; (void)A2tile_format; (void)A1tile_pos_rank; (void)A1tile_pos_ptr; (void)A1tile_crd_rank;    \
+    (void)A1tile_crd_ptr; (void)A2tile_pos_rank; (void)A2tile_pos_ptr; (void)A2tile_crd_rank; (void)A2tile_crd_ptr;  \
+    (void)B1tile_format; (void)B2tile_format; (void)B1tile_pos_rank; (void)B1tile_pos_ptr; (void)B1tile_crd_rank;    \
+    (void)B1tile_crd_ptr; (void)B2tile_pos_rank; (void)B2tile_pos_ptr; (void)B2tile_crd_rank; (void)B2tile_crd_ptr;  \
+    transpose_impl(ISZ, A1format, A2format, A1pos_rank, A1pos_ptr, A1crd_rank, A1crd_ptr, A2pos_rank, A2pos_ptr,     \
+                   A2crd_rank, A2crd_ptr, Aval_rank, Aval_ptr, B1format, B2format, B1pos_rank, B1pos_ptr,            \
+                   B1crd_rank, B1crd_ptr, B2pos_rank, B2pos_ptr, B2crd_rank, B2crd_ptr, Bval_rank, Bval_ptr,         \
+                   sizes_rank, sizes_ptr)
+
+extern "C" void comet_b200_transpose_2D_f64_i64(TRANSPOSE_ARGS) { TRANSPOSE_BODY(8); }
+extern "C" void comet_b200_transpose_2D_f64_i32(TRANSPOSE_ARGS) { TRANSPOSE_BODY(4); }

@@ -163,6 +163,34 @@ COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_to_dense_f64_i64(COMET_
                                                                           int64_t B_rank, void *B_ptr,
                                                                           int64_t C_rank, void *C_ptr);
 
+/* B = transpose(A) for a sparse matrix: replaces transpose_2D_f64_i64 of the reference runtime
+   (lib/ExecutionEngine/TransposeUtils.cpp:1439-1466) with the same argument list (memref ranks as int64_t):
+   the four format codes and the eight index memrefs of A, A's values, the same for B, and the `sizes` memref
+   whose first two entries are {rows, cols} of A and are swapped on return.  CSR -> CSR and COO -> COO, the
+   two pairs the reference handles; the caller has allocated B's arrays (B2pos of cols+1 entries for CSR). */
+COMET_B200_EXPORT void comet_b200_transpose_2D_f64_i64(
+    int32_t A1format, int32_t A1tile_format, int32_t A2format, int32_t A2tile_format, int64_t A1pos_rank,
+    void *A1pos_ptr, int64_t A1crd_rank, void *A1crd_ptr, int64_t A1tile_pos_rank, void *A1tile_pos_ptr,
+    int64_t A1tile_crd_rank, void *A1tile_crd_ptr, int64_t A2pos_rank, void *A2pos_ptr, int64_t A2crd_rank,
+    void *A2crd_ptr, int64_t A2tile_pos_rank, void *A2tile_pos_ptr, int64_t A2tile_crd_rank,
+    void *A2tile_crd_ptr, int64_t Aval_rank, void *Aval_ptr, int32_t B1format, int32_t B1tile_format,
+    int32_t B2format, int32_t B2tile_format, int64_t B1pos_rank, void *B1pos_ptr, int64_t B1crd_rank,
+    void *B1crd_ptr, int64_t B1tile_pos_rank, void *B1tile_pos_ptr, int64_t B1tile_crd_rank,
+    void *B1tile_crd_ptr, int64_t B2pos_rank, void *B2pos_ptr, int64_t B2crd_rank, void *B2crd_ptr,
+    int64_t B2tile_pos_rank, void *B2tile_pos_ptr, int64_t B2tile_crd_rank, void *B2tile_crd_ptr,
+    int64_t Bval_rank, void *Bval_ptr, int64_t sizes_rank, void *sizes_ptr);
+COMET_B200_EXPORT void comet_b200_transpose_2D_f64_i32(
+    int32_t A1format, int32_t A1tile_format, int32_t A2format, int32_t A2tile_format, int64_t A1pos_rank,
+    void *A1pos_ptr, int64_t A1crd_rank, void *A1crd_ptr, int64_t A1tile_pos_rank, void *A1tile_pos_ptr,
+    int64_t A1tile_crd_rank, void *A1tile_crd_ptr, int64_t A2pos_rank, void *A2pos_ptr, int64_t A2crd_rank,
+    void *A2crd_ptr, int64_t A2tile_pos_rank, void *A2tile_pos_ptr, int64_t A2tile_crd_rank,
+    void *A2tile_crd_ptr, int64_t Aval_rank, void *Aval_ptr, int32_t B1format, int32_t B1tile_format,
+    int32_t B2format, int32_t B2tile_format, int64_t B1pos_rank, void *B1pos_ptr, int64_t B1crd_rank,
+    void *B1crd_ptr, int64_t B1tile_pos_rank, void *B1tile_pos_ptr, int64_t B1tile_crd_rank,
+    void *B1tile_crd_ptr, int64_t B2pos_rank, void *B2pos_ptr, int64_t B2crd_rank, void *B2crd_ptr,
+    int64_t B2tile_pos_rank, void *B2tile_pos_ptr, int64_t B2tile_crd_rank, void *B2tile_crd_ptr,
+    int64_t Bval_rank, void *Bval_ptr, int64_t sizes_rank, void *sizes_ptr);
+
 /* Sparse-output operations use the two-call protocol COMET already uses for
    file input (read_input_sizes_2D_f64 then read_input_2D_f64_i64,
    lib/Dialect/TensorAlgebra/Transforms/TensorDeclLowering.cpp:937-1052): the
@@ -314,6 +342,29 @@ COMET_B200_EXPORT int32_t comet_b200_dev_sddmm_f64_i64(int64_t nrows, int64_t nn
                                                        const int64_t *crd, const double *sval,
                                                        const double *x, int64_t ldx, const double *y,
                                                        int64_t ldy, double *out, void *stream);
+
+/* Entries sorted by (major, minor); entries with equal coordinates keep their input order, as the
+   std::stable_sort of the reference reader does (lib/ExecutionEngine/SparseUtils.cpp:360-367; duplicates
+   are kept, not summed).  major_out / minor_out / vals_out may be NULL.  nmajor * nminor must fit 63 bits.
+   Synchronises the stream (it reports coordinates outside nmajor x nminor). */
+COMET_B200_EXPORT int32_t comet_b200_dev_sort_coo_f64_i64(int64_t n, int64_t nmajor, int64_t nminor,
+                                                          const int64_t *major, const int64_t *minor,
+                                                          const double *vals, int64_t *major_out,
+                                                          int64_t *minor_out, double *vals_out, void *stream);
+
+/* Coordinate entries in any order -> CSR arrays (pos[nrows+1], crd[nnz], val[nnz]) in the order the reference
+   reader builds them (CooMatrix sort + CsrMatrix::Init, lib/ExecutionEngine/SparseUtils.cpp:360-533). */
+COMET_B200_EXPORT int32_t comet_b200_dev_coo_to_csr_f64_i64(int64_t nrows, int64_t ncols, int64_t nnz,
+                                                            const int64_t *rows, const int64_t *cols,
+                                                            const double *vals, int64_t *pos, int64_t *crd,
+                                                            double *val, void *stream);
+
+/* CSR of the transposed matrix: tpos[ncols+1], tcrd[nnz] (row indices of the input, ascending inside a
+   column), tval[nnz].  The CSR -> CSR branch of transpose_2D (lib/ExecutionEngine/TransposeUtils.cpp:738-812). */
+COMET_B200_EXPORT int32_t comet_b200_dev_csr_transpose_f64_i64(int64_t nrows, int64_t ncols, int64_t nnz,
+                                                               const int64_t *pos, const int64_t *crd,
+                                                               const double *val, int64_t *tpos, int64_t *tcrd,
+                                                               double *tval, void *stream);
 
 /* dst[j, i] = src[i, j] for a row-major [rows, cols] src (used to bring a D[k,j]
    operand into the [cols, K] layout the SDDMM kernel gathers from). */

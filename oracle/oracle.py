@@ -204,6 +204,28 @@ def elews_sparse_dense(A, B):
     return out
 
 
+def transpose(A):
+    """Transpose of a CSR or COO matrix in the same format: the entries ordered by (column, row) of
+    the input, the CSR -> COO -> sort -> CSR route of transpose_2D
+    (lib/ExecutionEngine/TransposeUtils.cpp:738-812; COO: :625-697).  Entries with equal coordinates
+    keep their input order."""
+    if A.format == "CSR":
+        rows = np.repeat(np.arange(A.nrows, dtype=np.int64), np.diff(_i64(A.a2pos)))
+    elif A.format == "COO":
+        rows = _i64(A.a1crd)
+    else:
+        raise ValueError("transpose: CSR and COO")
+    cols = _i64(A.a2crd)
+    order = np.lexsort((rows, cols))                     # stable: by column, then row, then position
+    if A.format == "COO":
+        return SparseArrays("COO", A.ncols, A.nrows, np.array([0, A.nnz], dtype=np.int64), cols[order],
+                            np.array([-1], dtype=np.int64), rows[order], A.val[order])
+    pos = np.zeros(A.ncols + 1, dtype=np.int64)
+    np.cumsum(np.bincount(cols, minlength=A.ncols), out=pos[1:])
+    return SparseArrays("CSR", A.ncols, A.nrows, np.array([A.ncols], dtype=np.int64), np.array([-1], dtype=np.int64),
+                        pos, rows[order], A.val[order])
+
+
 def elews_sparse_dense_to_dense(A, B, C0=None):
     """Dense result of ta.elews_mul with one sparse operand: products at the stored positions
     (lib/Conversion/IndexTreeToSCF/IndexTreeToSCF.cpp:1247-1284 with the "noop" reduce)."""

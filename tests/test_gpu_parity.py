@@ -493,3 +493,62 @@ def test_elews_sparse_dense_to_dense(fmt, tmp_path):
     assert np.array_equal(api.elews_sparse_dense_to_dense(A, B, C0), oracle.elews_sparse_dense_to_dense(A, B, C0))
     A32 = api.as_sparse(A).with_index_dtype(np.int32)
     assert np.array_equal(api.elews_sparse_dense_to_dense(A32, B), oracle.elews_sparse_dense_to_dense(A, B))
+
+
+def test_device_coo_to_csr_reproduces_the_reader_goldens(golden, mtx_dir):
+    """The reader sorts the parsed entries on the host; the device sort must give the same CSR arrays.
+    Every CSR reader test of the reference is replayed: the entries (as the reader keeps them, read mode
+    applied) are shuffled, sorted on the device, printed and compared with the CHECK lines."""
+    import os
+    rng = np.random.default_rng(11)
+    n = 0
+    for name, case in golden["cases"].items():
+        if case["kind"] != "reader":
+            continue
+        (tname, r), = case["reads"].items()
+        if case["tensors"][tname]["format"] != "CSR":
+            continue
+        path = os.path.join(mtx_dir, case["files"][r["file_id"]])
+        coo = oracle.read_mtx(path, "COO", r["read_mode"])
+        perm = rng.permutation(coo.nnz)
+        got = api.from_coordinates(np.asarray(coo.a1crd)[perm], np.asarray(coo.a2crd)[perm], coo.val[perm],
+                                   (coo.nrows, coo.ncols))
+        text = "".join(oracle.print_memref(a) for a in (got.a1pos, got.a1crd, got.a2pos, got.a2crd, got.val))
+        want = oracle.read_mtx(path, "CSR", r["read_mode"])
+        assert text == "".join(oracle.print_memref(a) for a in (want.a1pos, want.a1crd, want.a2pos, want.a2crd, want.val))
+        assert [l for l in text.splitlines() if l.strip() and not l.startswith("data")] == \
+               [c for c in case["checks"] if not c.startswith("data")]
+        n += 1
+    assert n >= 5
+    # equal coordinates keep their input order (values tell them apart)
+    rows = np.array([2, 0, 2, 1, 2, 0]); cols = np.array([1, 3, 1, 0, 1, 3]); vals = np.arange(6.0)
+    got = api.from_coordinates(rows, cols, vals, (3, 4))
+    assert got.a2pos.tolist() == [0, 2, 3, 6] and got.a2crd.tolist() == [3, 3, 0, 1, 1, 1]
+    assert got.val.tolist() == [1.0, 5.0, 3.0, 0.0, 2.0, 4.0]
+
+
+@pytest.mark.parametrize("index_dtype", [np.int64, np.int32])
+def test_sparse_transpose(index_dtype, tmp_path):
+    A = _skewed(1500, seed=13).with_index_dtype(index_dtype)
+    T = api.transpose(A)
+    ref = oracle.transpose(_orc(A))
+    assert (T.nrows, T.ncols) == (ref.nrows, ref.ncols)
+    assert T.a2pos.dtype == index_dtype and T.a2crd.dtype == index_dtype
+    assert np.array_equal(T.a2pos, ref.a2pos) and np.array_equal(T.a2crd, ref.a2crd) and np.array_equal(T.val, ref.val)
+    want = A.to_scipy().T.tocsr()
+    want.sort_indices()
+    assert np.array_equal(T.a2pos, want.indptr) and np.array_equal(T.a2crd, want.indices)
+    # rectangular, with empty rows and columns; twice transposed is the matrix itself
+    R = api.as_sparse(sp.random(300, 7000, density=0.001, random_state=np.random.default_rng(5), format="csr"))
+    RT = api.transpose(R)
+    assert (RT.nrows, RT.ncols) == (7000, 300)
+    RTT = api.transpose(RT)
+    assert np.array_equal(RTT.a2pos, R.a2pos) and np.array_equal(RTT.a2crd, R.a2crd) and np.array_equal(RTT.val, R.val)
+    # COO -> COO
+    path = tmp_path / "a.mtx"
+    datasets.write_mtx(str(path), A)
+    C = oracle.read_mtx(str(path), "COO")
+    TC = api.transpose(C)
+    rc = oracle.transpose(C)
+    assert np.array_equal(TC.a1crd, rc.a1crd) and np.array_equal(TC.a2crd, rc.a2crd) and np.array_equal(TC.val, rc.val)
+    assert TC.a1pos.tolist() == [0, C.nnz]

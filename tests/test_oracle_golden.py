@@ -51,3 +51,26 @@ def test_oracle_against_scipy_random():
     X = rng.uniform(-1, 1, (200, 9)); Y = rng.uniform(-1, 1, (150, 9))
     want = np.asarray(A.multiply(X @ Y.T).tocsr()[A.nonzero()]).ravel()
     np.testing.assert_allclose(oracle.sddmm(oa, X, Y), want, rtol=1e-12, atol=1e-14)
+
+
+def test_transpose_restatement_against_scipy():
+    """No reference test prints a transposed sparse matrix, so this piece of the oracle is held against
+    scipy instead: CSR and COO, duplicates kept in input order."""
+    import scipy.sparse as sp
+    rng = np.random.default_rng(7)
+    m = sp.random(60, 45, density=0.1, random_state=rng, format="csr")
+    m.sort_indices()
+    A = oracle.SparseArrays("CSR", 60, 45, np.array([60]), np.array([-1]), m.indptr.astype(np.int64),
+                            m.indices.astype(np.int64), m.data.copy())
+    T = oracle.transpose(A)
+    want = m.T.tocsr()
+    want.sort_indices()
+    assert (T.nrows, T.ncols) == (45, 60)
+    assert np.array_equal(T.a2pos, want.indptr) and np.array_equal(T.a2crd, want.indices)
+    assert np.array_equal(T.val, want.data)
+    # COO with a repeated coordinate: both copies survive, first one first
+    C = oracle.SparseArrays("COO", 3, 4, np.array([0, 4]), np.array([0, 1, 1, 2]), np.array([-1]),
+                            np.array([2, 3, 3, 0]), np.array([1.0, 2.0, 3.0, 4.0]))
+    Tc = oracle.transpose(C)
+    assert Tc.a1crd.tolist() == [0, 2, 3, 3] and Tc.a2crd.tolist() == [2, 0, 1, 1]
+    assert Tc.val.tolist() == [4.0, 1.0, 2.0, 3.0]
