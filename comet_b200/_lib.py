@@ -36,6 +36,8 @@ SIGNATURES = {
     "comet_b200_spgemm_numeric_f64_i64": (None, [c_int64] + _MEMREF * 2),
     "comet_b200_elews_mul_sparse_sparse_symbolic_f64_i64": (c_int64, _SPARSE * 2 + _MEMREF * 2),
     "comet_b200_transpose_2D_f64_i64": (None, ([c_int32] * 4 + [c_int64, c_void_p] * 9) * 2 + _MEMREF),
+    "comet_b200_read_input_sizes_2D_f64": (None, [c_int32] * 5 + _MEMREF + [c_int32]),
+    "comet_b200_read_input_2D_f64_i64": (None, [c_int32] * 5 + [c_int64, c_void_p] * 9 + [c_int32]),
     "comet_b200_handle_destroy": (None, [c_int64]),
     "comet_b200_masked_spgemm_count_f64_i64": (None, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF),
     "comet_b200_last_error": (ctypes.c_char_p, []),

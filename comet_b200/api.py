@@ -354,6 +354,30 @@ def transpose(A):
     return SparseTensor(A.format, int(sizes[0]), int(sizes[1]), b1pos, b1crd, b2pos, b2crd, bval)
 
 
+def read_mtx(path, fmt="CSR", read_mode=1, index_dtype=np.int64, file_id=0):
+    """MatrixMarket file -> COMET arrays through the two reader entry points (sizes, then fill), the way
+    generated code calls read_input_sizes_2D_f64 / read_input_2D_f64_i64
+    (lib/Conversion/TensorAlgebraToSCF/TensorDeclLowering.cpp:937-1052).  The sort runs on the device."""
+    import os
+    lib = _lib.load()
+    os.environ["SPARSE_FILE_NAME%d" % file_id] = os.fspath(path)
+    f1, f2 = _FMT[fmt]
+    pk = _Packer()
+    sizes = np.zeros(11, dtype=np.int64)
+    lib.comet_b200_read_input_sizes_2D_f64(file_id, f1, -1, f2, -1, *pk.m1(sizes), int(read_mode))
+    _lib.check()
+    dt = np.dtype(index_dtype)
+    arrs = [np.zeros(max(int(sizes[i]), 1), dtype=dt) for i in (0, 1, 4, 5)]
+    val = np.zeros(max(int(sizes[8]), 1))
+    empty = np.zeros(0, dtype=dt)
+    fn = lib.comet_b200_read_input_2D_f64_i32 if dt == np.int32 else lib.comet_b200_read_input_2D_f64_i64
+    fn(file_id, f1, -1, f2, -1, *pk.m1(arrs[0]), *pk.m1(arrs[1]), *pk.m1(empty), *pk.m1(empty), *pk.m1(arrs[2]),
+       *pk.m1(arrs[3]), *pk.m1(empty), *pk.m1(empty), *pk.m1(val), int(read_mode))
+    _lib.check()
+    return SparseTensor(fmt, int(sizes[9]), int(sizes[10]), arrs[0][:int(sizes[0])], arrs[1][:int(sizes[1])],
+                        arrs[2][:int(sizes[4])], arrs[3][:int(sizes[5])], val[:int(sizes[8])])
+
+
 def from_coordinates(rows, cols, vals, shape):
     """CSR from coordinate entries in any order, sorted on the device the way the reference reader sorts
     them on the host (by row, then column; entries with equal coordinates stay in input order and are

@@ -163,6 +163,28 @@ COMET_B200_EXPORT void comet_b200_elews_mul_sparse_dense_to_dense_f64_i64(COMET_
                                                                           int64_t B_rank, void *B_ptr,
                                                                           int64_t C_rank, void *C_ptr);
 
+/* The MatrixMarket reader with its sort on the device: same argument lists as read_input_sizes_2D_f64 and
+   read_input_2D_f64_{i64,i32} (lib/ExecutionEngine/SparseUtils.cpp:2427-2450, 2562-2568; memref ranks as
+   int64_t).  The file is named by the environment variable SPARSE_FILE_NAME<fileID> (SPARSE_FILE_NAME for
+   fileID 9999).  The sizes call fills the 11-entry array {A1pos, A1crd, A1tile_pos, A1tile_crd, A2pos, A2crd,
+   A2tile_pos, A2tile_crd, nnz, rows, cols}; the caller allocates and the second call fills.  readMode:
+   1 all entries, 2 strictly lower triangle, 3 lower, 4 strictly upper, 5 upper (CSR and COO; DCSR keeps all). */
+COMET_B200_EXPORT void comet_b200_read_input_sizes_2D_f64(int32_t fileID, int32_t A1format, int32_t A1tile_format,
+                                                          int32_t A2format, int32_t A2tile_format,
+                                                          int64_t sizes_rank, void *sizes_ptr, int32_t readMode);
+COMET_B200_EXPORT void comet_b200_read_input_2D_f64_i64(
+    int32_t fileID, int32_t A1format, int32_t A1tile_format, int32_t A2format, int32_t A2tile_format,
+    int64_t A1pos_rank, void *A1pos_ptr, int64_t A1crd_rank, void *A1crd_ptr, int64_t A1tile_pos_rank,
+    void *A1tile_pos_ptr, int64_t A1tile_crd_rank, void *A1tile_crd_ptr, int64_t A2pos_rank, void *A2pos_ptr,
+    int64_t A2crd_rank, void *A2crd_ptr, int64_t A2tile_pos_rank, void *A2tile_pos_ptr, int64_t A2tile_crd_rank,
+    void *A2tile_crd_ptr, int64_t Aval_rank, void *Aval_ptr, int32_t readMode);
+COMET_B200_EXPORT void comet_b200_read_input_2D_f64_i32(
+    int32_t fileID, int32_t A1format, int32_t A1tile_format, int32_t A2format, int32_t A2tile_format,
+    int64_t A1pos_rank, void *A1pos_ptr, int64_t A1crd_rank, void *A1crd_ptr, int64_t A1tile_pos_rank,
+    void *A1tile_pos_ptr, int64_t A1tile_crd_rank, void *A1tile_crd_ptr, int64_t A2pos_rank, void *A2pos_ptr,
+    int64_t A2crd_rank, void *A2crd_ptr, int64_t A2tile_pos_rank, void *A2tile_pos_ptr, int64_t A2tile_crd_rank,
+    void *A2tile_crd_ptr, int64_t Aval_rank, void *Aval_ptr, int32_t readMode);
+
 /* B = transpose(A) for a sparse matrix: replaces transpose_2D_f64_i64 of the reference runtime
    (lib/ExecutionEngine/TransposeUtils.cpp:1439-1466) with the same argument list (memref ranks as int64_t):
    the four format codes and the eight index memrefs of A, A's values, the same for B, and the `sizes` memref

@@ -46,6 +46,23 @@ def test_no_cpu_fallback_without_a_device():
         comet_b200.spmv(A, np.ones(8))
 
 
+def test_reader_needs_a_device_and_reports_bad_files(tmp_path):
+    import torch
+    import comet_b200.api as api
+    from comet_b200._lib import CometB200Error
+    with pytest.raises(CometB200Error, match="cannot open"):
+        api.read_mtx(str(tmp_path / "missing.mtx"))
+    bad = tmp_path / "bad.mtx"
+    bad.write_text("%%MatrixMarket matrix coordinate real general\n2 2 1\n3 1 1.0\n")
+    with pytest.raises(CometB200Error, match="outside"):
+        api.read_mtx(str(bad))
+    if not torch.cuda.is_available():
+        ok = tmp_path / "ok.mtx"
+        ok.write_text("%%MatrixMarket matrix coordinate real general\n2 2 1\n2 1 1.0\n")
+        with pytest.raises(CometB200Error, match="no CUDA device"):
+            api.read_mtx(str(ok))
+
+
 def test_bad_descriptors_are_rejected_on_the_host():
     import comet_b200
     from comet_b200._lib import CometB200Error
