@@ -70,11 +70,16 @@ spmm_stream_plan_kernel(int64_t nrows, int64_t nnz, int64_t q, int64_t nblocks, 
     for (int64_t b = warp; b <= nblocks; b += nwarps) {
         int64_t d = b * q;
         if (d > nnz + nrows) d = nnz + nrows;
-        int64_t lo = 0, hi = nrows;                    // largest r in [0, nrows] with pos[r] + r <= d
+        // largest r in [0, nrows] with pos[r] + r <= d: the 32 lanes probe 32 points of the range per step
+        int64_t lo = 0, hi = nrows;
         while (lo < hi) {
-            const int64_t mid = (lo + hi + 1) >> 1;
-            if (pos[mid] + mid <= d) lo = mid;
-            else hi = mid - 1;
+            const int64_t step = (hi - lo + 31) / 32;
+            int64_t probe = lo + (lane + 1) * step;
+            if (probe > hi) probe = hi;
+            const int k = __popc(__ballot_sync(0xffffffffu, pos[probe] + probe <= d));   // the first k probes hold
+            const int64_t fail_at = lo + (int64_t)(k + 1) * step;                             // probe k does not (if k < 32)
+            if (k > 0) { lo += (int64_t)k * step; if (lo > hi) lo = hi; }
+            if (k < 32) hi = (fail_at < hi ? fail_at : hi) - 1;                               // the answer lies before probe k
         }
         int64_t r = lo, e = d - lo;
         if (b > 0 && r < nrows && e >= pos[r + 1]) {   // the boundary is the end of row r: start at the next row
