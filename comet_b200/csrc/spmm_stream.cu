@@ -22,6 +22,7 @@
 //
 // Bound: HBM.  Algorithmic bytes = 8(n+1) + 16 nnz + 8 ncols K + 8 nrows K.
 #include "common.cuh"
+#include "stream.cuh"
 
 namespace cb200 {
 
@@ -30,29 +31,6 @@ static const int SB_G = 4;                     // rows of B per stage (one copy 
 static const int SB_MAX_STAGES = 8;
 static const int SB_RING_BYTES = 12 * 1024;    // per warp
 static const int SB_SIDE_BYTES = 512;           // per warp: 32 column indices, 32 values of A, 32 row ends
-
-__device__ __forceinline__ uint32_t sb_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-// 16 bytes global -> shared without passing through registers or L1
-__device__ __forceinline__ void sb_copy16(uint32_t dst, const void *src)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void sb_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// wait until at most `pending` of this thread's copy groups are still in flight
-__device__ __forceinline__ void sb_wait_pending(int pending)
-{
-    switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
-    }
-}
 
 // Blocks are equal pieces of the path that walks A row by row: one step per stored entry and one
 // step per row end (a row costs about as much as an entry: its result is written, or zeros for an
@@ -309,6 +287,34 @@ spmm_stream_kernel(int64_t nrows, int64_t nnz, int64_t q, unsigned nblocks, cons
     }
 }
 
+// Cuts the (entries + rows) path of a CSR matrix into pieces for `warps` persistent warps and runs the plan
+// kernel.  c != null and accumulate == 0: rows cut by a boundary get zeros (k columns).  Returns 1, 0 when the
+// piece count does not fit 32 bits, -1 on error.  The plan lives in the work-list scratch slot of the device.
+int stream_plan(int64_t nrows, int64_t nnz, int64_t warps, const int64_t *row_ids, const int64_t *pos, double *c,
+                int64_t ldc, int k, int accumulate, cudaStream_t st, StreamPlan *out)
+{
+    const int64_t steps = nnz + nrows;                 // path length: one step per entry, one per row end
+    int64_t q = ceil_div(steps, warps * 8);
+    if (q < 512) q = 512;
+    const int64_t nblocks = ceil_div(steps, q);
+    if (nblocks > 0x7ffffff0LL) return 0;
+    void *wl = nullptr;
+    if (scratch(SLOT_WORKLIST, sizeof(WorkHeader) + (size_t)(nblocks + 1) * 2 * sizeof(int64_t), &wl)) return -1;
+    out->hdr = (WorkHeader *)wl;
+    out->block_row = (int64_t *)((char *)wl + sizeof(WorkHeader));
+    out->block_ent = out->block_row + (nblocks + 1);
+    out->q = q;
+    out->nblocks = nblocks;
+    if (cudaMemsetAsync(out->hdr, 0, sizeof(WorkHeader), st) != cudaSuccess) {
+        fail("clearing the block counter failed");
+        return -1;
+    }
+    const int64_t pgrid = ceil_div((nblocks + 1) * 32, 256);
+    spmm_stream_plan_kernel<<<(unsigned)pgrid, 256, 0, st>>>(nrows, nnz, q, nblocks, row_ids, pos, c, ldc, k,
+                                                            c ? accumulate : 1, out->block_row, out->block_ent);
+    return 1;
+}
+
 // Returns 1 when this path took the call, 0 when the shape is not one it handles, -1 on error.
 int spmm_stream(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_t *row_ids, const int64_t *pos,
                 const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
@@ -323,25 +329,13 @@ int spmm_stream(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int6
     if (stages < 2) return 0;
     const size_t smem = (size_t)SB_WARPS * ((size_t)stages * SB_G * rowbytes + SB_SIDE_BYTES);
 
-    const int64_t warps = (int64_t)sm_count() * SB_WARPS;
-    const int64_t steps = nnz + nrows;                 // path length: one step per entry, one per row end
-    int64_t q = ceil_div(steps, warps * 8);
-    if (q < 512) q = 512;
-    const int64_t nblocks = ceil_div(steps, q);
-    if (nblocks > 0x7ffffff0LL) return 0;
-
-    void *wl = nullptr;
-    if (scratch(SLOT_WORKLIST, sizeof(WorkHeader) + (size_t)(nblocks + 1) * 2 * sizeof(int64_t), &wl)) return -1;
-    WorkHeader *hdr = (WorkHeader *)wl;
-    int64_t *block_row = (int64_t *)((char *)wl + sizeof(WorkHeader));
-    int64_t *block_ent = block_row + (nblocks + 1);
-    if (cudaMemsetAsync(hdr, 0, sizeof(WorkHeader), st) != cudaSuccess) {
-        fail("spmm: clearing the block counter failed");
-        return -1;
-    }
-    int64_t pgrid = ceil_div((nblocks + 1) * 32, 256);
-    spmm_stream_plan_kernel<<<(unsigned)pgrid, 256, 0, st>>>(nrows, nnz, q, nblocks, row_ids, pos, c, ldc, (int)k,
-                                                            accumulate, block_row, block_ent);
+    StreamPlan plan;
+    const int planned = stream_plan(nrows, nnz, (int64_t)sm_count() * SB_WARPS, row_ids, pos, c, ldc, (int)k, accumulate,
+                                    st, &plan);
+    if (planned <= 0) return planned;
+    WorkHeader *hdr = plan.hdr;
+    const int64_t *block_row = plan.block_row, *block_ent = plan.block_ent;
+    const int64_t q = plan.q, nblocks = plan.nblocks;
     int64_t grid = ceil_div(nblocks, SB_WARPS);
     if (grid > sm_count()) grid = sm_count();
     const int ni = k <= 64 ? 1 : (k <= 128 ? 2 : 4);

@@ -599,3 +599,13 @@ def test_reader_entry_points_reproduce_the_reader_goldens(golden, mtx_dir, tmp_p
     x = datasets.dense_uniform(A.ncols, 1)
     ref = oracle.spmv(oracle.read_mtx(str(path), "CSR"), x)
     _close(api.spmv(A, x), ref, np.abs(ref) + 1.0)
+
+
+@pytest.mark.parametrize("k", [64, 128])
+def test_sddmm_empty_rows_and_a_hub_row(k):
+    """Empty rows at every position, single-entry rows and a row far longer than a chunk, at a size where
+    both SDDMM kernels (entry stream for short rows, chunk list for long ones) carry work."""
+    S = _gappy(n=70000, seed=8)
+    X = datasets.dense_uniform((S.nrows, k), 1)
+    Y = datasets.dense_uniform((S.ncols, k), 2)
+    _close(api.sddmm(S, X, Y), oracle.sddmm(_orc(S), X, Y), oracle.sddmm(_abs(S), np.abs(X), np.abs(Y)))
