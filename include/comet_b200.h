@@ -322,8 +322,13 @@ COMET_B200_EXPORT int32_t comet_b200_dev_spmv_f64_i64(int64_t nrows, int64_t nnz
                                                       int32_t semiring, int32_t accumulate,
                                                       void *stream);
 
-/* variant: 0 = automatic; otherwise (panel width in columns) | (lanes per row << 16),
-   the number of B columns handled per pass over A and the lane-group size, for tuning. */
+/* variant: 0 = automatic.  Bits 24-25 pick the kernel family: 0 = by shape (the entry-stream kernel
+   from 64 columns and 65536 stored entries on, for plus-times; the row-panel kernels otherwise),
+   1 = entry stream whenever the shape allows it (K even, at most 256; worth asking for with
+   narrow B and a power-law A, where it is several times faster than the panels),
+   2 = row panels.  For the row panels the low bits are (panel width in columns) |
+   (lanes per row << 16): the number of B columns handled per pass over A and the lane-group
+   size, for tuning. */
 COMET_B200_EXPORT int32_t comet_b200_dev_spmm_f64_i64(int64_t nrows, int64_t ncols, int64_t nnz,
                                                       int64_t k,
                                                       const int64_t *row_ids, const int64_t *pos,
