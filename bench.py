@@ -36,7 +36,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one step's kernels at the default (full) size on one
 # GPU, from the one-pass ncu captures summarised under profiles/.  Reported as roofline.traffic only
 # when the run uses exactly that workload.
-NCU_DRAM_BYTES_PER_STEP = {"spmm": 6.063e9, "sddmm": 0.488e9, "spgemm": 77.2e9, "triangles": 25.2e9}
+NCU_DRAM_BYTES_PER_STEP = {"spmm": 6.063e9, "sddmm": 0.488e9, "spgemm": 50.6e9, "triangles": 25.2e9}
 
 
 def measured_peak():
