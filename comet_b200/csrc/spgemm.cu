@@ -157,6 +157,7 @@ __device__ __forceinline__ void sr_fold(int semi, double *addr, double v)
 // --------------------------------------------------------------------------
 static const int BIN_THREADS = 256;
 static const int BIN_ROWS = (BIN_THREADS / 8) * 4;
+static const int64_t BIN_LONG_ROW = 1024;
 
 __global__ void __launch_bounds__(BIN_THREADS)
 bin_rows_kernel(int64_t nrows, const int64_t *__restrict__ apos, const int64_t *__restrict__ acrd,
@@ -166,33 +167,66 @@ bin_rows_kernel(int64_t nrows, const int64_t *__restrict__ apos, const int64_t *
 {
     __shared__ unsigned char bin_of[BIN_ROWS];
     __shared__ unsigned short local_at[BIN_ROWS];
-    __shared__ unsigned local_cnt[2], base[2];
+    __shared__ unsigned local_cnt[2], base[2], n_long;
+    __shared__ unsigned short long_slot[BIN_ROWS];
+    __shared__ int64_t warp_sum[BIN_THREADS / 32];
     const int g = threadIdx.x / 8, l = threadIdx.x % 8;
     const unsigned gmask = 0xffu << ((threadIdx.x & 31) & ~7);
     if (threadIdx.x < 2) local_cnt[threadIdx.x] = 0;
+    if (threadIdx.x == 2) n_long = 0;
     __syncthreads();
     const int64_t row0 = (int64_t)blockIdx.x * BIN_ROWS;
+    // the bin of a row from the upper bound ub of its distinct columns
+    auto place = [&](int slot, int64_t r, int64_t ub) {
+        if (mpos) {
+            int64_t ml = mpos[r + 1] - mpos[r];
+            if (ml < ub) ub = ml;
+        }
+        int b = ub == 0 ? 0 : (ub <= HASH_ROW_MAX ? 1 : 2);
+        bin_of[slot] = (unsigned char)b;
+        if (b == 0) cnt[r] = 0;
+        else local_at[slot] = (unsigned short)atomicAdd(&local_cnt[b - 1], 1u);
+    };
     for (int pass = 0; pass < 4; pass++) {
         int slot = pass * (BIN_THREADS / 8) + g;
         int64_t r = row0 + slot;
         if (r >= nrows) break;
+        const int64_t as = apos[r], ae = apos[r + 1];
+        if (ae - as > BIN_LONG_ROW) {                    // a hub row: left to the whole CTA below
+            if (l == 0) long_slot[atomicAdd(&n_long, 1u)] = (unsigned short)slot;
+            continue;
+        }
         int64_t ub = 0;
-        for (int64_t p = apos[r] + l; p < apos[r + 1]; p += 8) {
+        for (int64_t p = as + l; p < ae; p += 8) {
             int64_t k = acrd[p];
             ub += bpos[k + 1] - bpos[k];
         }
 #pragma unroll
         for (int o = 4; o > 0; o >>= 1) ub += __shfl_xor_sync(gmask, (long long)ub, o, 8);
-        if (mpos) {
-            int64_t ml = mpos[r + 1] - mpos[r];
-            if (ml < ub) ub = ml;
+        if (l == 0) place(slot, r, ub);
+    }
+    __syncthreads();
+    // rows of A with thousands of entries: eight lanes would walk them for a millisecond while the rest of
+    // the grid has finished
+    const unsigned nl = n_long;
+    for (unsigned i = 0; i < nl; i++) {
+        const int slot = long_slot[i];
+        const int64_t r = row0 + slot;
+        int64_t ub = 0;
+        for (int64_t p = apos[r] + threadIdx.x; p < apos[r + 1]; p += BIN_THREADS) {
+            int64_t k = acrd[p];
+            ub += bpos[k + 1] - bpos[k];
         }
-        if (l == 0) {
-            int b = ub == 0 ? 0 : (ub <= HASH_ROW_MAX ? 1 : 2);
-            bin_of[slot] = (unsigned char)b;
-            if (b == 0) cnt[r] = 0;
-            else local_at[slot] = (unsigned short)atomicAdd(&local_cnt[b - 1], 1u);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ub += __shfl_xor_sync(0xffffffffu, (long long)ub, o);
+        if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = ub;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int64_t t = 0;
+            for (int w = 0; w < BIN_THREADS / 32; w++) t += warp_sum[w];
+            place(slot, r, t);
         }
+        __syncthreads();
     }
     __syncthreads();
     if (threadIdx.x < 2) base[threadIdx.x] = atomicAdd(&bin_counts[threadIdx.x], local_cnt[threadIdx.x]);
@@ -406,7 +440,7 @@ __device__ __forceinline__ void mark_products(uint32_t *bm, int64_t r, const int
     for_each_product(r, 0u, 1u, apos, acrd, nullptr, bpos, s_long, s_ctl, [&](int64_t q, double) {
         int32_t j = bcrd[q];
         if (mpos && !in_mask(mcrd, ms, me, j)) return;
-        atomicOr(&bm[j >> 5], 1u << (j & 31));
+        atomicOr(&bm[j >> 5], 1u << (j & 31));          // testing the bit first was measured slower (6.4 vs 5.2 ms)
     });
 }
 
