@@ -40,6 +40,20 @@ SIGNATURES = {
     "comet_b200_read_input_2D_f64_i64": (None, [c_int32] * 5 + [c_int64, c_void_p] * 9 + [c_int32]),
     "comet_b200_handle_destroy": (None, [c_int64]),
     "comet_b200_masked_spgemm_count_f64_i64": (None, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF),
+    # several GPUs: communicator, sharded host entry points, device-layer collectives
+    "comet_b200_comm_unique_id": (c_int32, [c_void_p, c_int64]),
+    "comet_b200_comm_init": (c_int32, [c_int32, c_int32, c_void_p]),
+    "comet_b200_comm_nranks": (c_int32, []),
+    "comet_b200_comm_rank": (c_int32, []),
+    "comet_b200_comm_destroy": (c_int32, []),
+    "comet_b200_comm_slice_bytes": (c_int64, [c_int64, c_int32]),
+    "comet_b200_spmm_sharded_f64_i64": (None, _SPARSE + _MEMREF * 2 + [c_int32, c_int32]),
+    "comet_b200_sddmm_sharded_f64_i64": (None, _SPARSE + _MEMREF * 2 + _SPARSE),
+    "comet_b200_spgemm_symbolic_sharded_f64_i64": (c_int64, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF * 2),
+    "comet_b200_masked_spgemm_count_sharded_f64_i64": (None, _SPARSE * 3 + [c_int32, c_int32] + _MEMREF),
+    "comet_b200_dev_allreduce_sum_i64": (c_int32, [c_void_p, c_int64, c_void_p]),
+    "comet_b200_dev_allgather_i64": (c_int32, [c_void_p, c_void_p, c_void_p]),
+    "comet_b200_dev_allgather_slices": (c_int32, [c_void_p, c_int64, c_void_p]),
     "comet_b200_last_error": (ctypes.c_char_p, []),
     "comet_b200_set_error_mode": (None, [c_int32]),
     "comet_b200_version": (c_int32, []),

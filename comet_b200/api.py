@@ -190,14 +190,21 @@ def spmv(A, x, y0=None, semiring=PLUS_TIMES):
     return y
 
 
-def spmm(A, B, C0=None, semiring=PLUS_TIMES):
+def _name(op, sharded):
+    """``sharded``: the collective form of the call, under the communicator set up by
+    ``sharding.init_library_comm``: the left operand, mask and result are this rank's row block, the right
+    operand is the whole matrix (identical on every rank)."""
+    return op + "_sharded" if sharded else op
+
+
+def spmm(A, B, C0=None, semiring=PLUS_TIMES, sharded=False):
     """C = C0 + A @ B  (ta.mul, sparse x dense matrix), B row-major."""
     A = as_sparse(A)
     lib = _lib.load()
     pk = _Packer()
     B = _f64(B)
     C = np.zeros((A.nrows, B.shape[1])) if C0 is None else _f64(C0).copy()
-    fn, _, (A,) = _entry(lib, "spmm", A)
+    fn, _, (A,) = _entry(lib, _name("spmm", sharded), A)
     fn(*pk.sparse(A), *pk.m2(B), *pk.m2(C), _dense_semiring(semiring), 0 if C0 is None else 1)
     _lib.check()
     return C
@@ -220,7 +227,7 @@ def dense_times_sparse(A, B, C0=None, semiring=PLUS_TIMES):
     return C
 
 
-def sddmm(S, X, Y, y_is_kj=False):
+def sddmm(S, X, Y, y_is_kj=False, sharded=False):
     """values of S .* (X @ Y^T) on S's pattern.  Y is [cols, K] row-major, or the
     [K, cols] operand D[k,j] of the reference's sddmm.ta when ``y_is_kj``."""
     S = as_sparse(S)
@@ -230,7 +237,7 @@ def sddmm(S, X, Y, y_is_kj=False):
     out = SparseTensor("CSR", S.nrows, S.ncols, np.zeros_like(S.a1pos), np.zeros_like(S.a1crd),
                        np.zeros_like(S.a2pos), np.zeros_like(S.a2crd), np.zeros(S.nnz))
     d_args = pk.m2(Y) if y_is_kj else pk.m2(Y, transposed_view=True)
-    fn, _, _unused = _entry(lib, "sddmm", S)
+    fn, _, _unused = _entry(lib, _name("sddmm", sharded), S)
     fn(*pk.sparse(S), *pk.m2(X), *d_args, *pk.sparse(out))
     _lib.check()
     assert np.array_equal(out.a2pos, S.a2pos) and np.array_equal(out.a2crd, S.a2crd)
@@ -278,18 +285,22 @@ def _finish_sparse_out(lib, handle, nrows, ncols, cpos, sizes):
                         cval)
 
 
-def spgemm(A, B, M=None, semiring=PLUS_TIMES):
-    """C = A @ B, or C<M,push> = A @ B, all CSR; returns a CSR SparseTensor."""
+def spgemm(A, B, M=None, semiring=PLUS_TIMES, sharded=False):
+    """C = A @ B, or C<M,push> = A @ B, all CSR; returns a CSR SparseTensor.  With ``sharded`` the
+    result is this rank's row block and carries ``entry_offset`` / ``total_nnz`` (its place in the whole C)."""
     A, B = as_sparse(A), as_sparse(B)
     Mt = as_sparse(M) if M is not None else A
     lib = _lib.load()
     pk = _Packer()
-    fn, dt, (A, B, Mt) = _entry(lib, "spgemm_symbolic", A, B, Mt)
+    fn, dt, (A, B, Mt) = _entry(lib, _name("spgemm_symbolic", sharded), A, B, Mt)
     cpos = np.zeros(A.nrows + 1, dtype=dt)
-    sizes = np.zeros(11, dtype=np.int64)
+    sizes = np.zeros(13, dtype=np.int64)
     handle = fn(*pk.sparse(A), *pk.sparse(B), *pk.sparse(Mt), MASK_PUSH if M is not None else MASK_NONE,
                 _semiring(semiring), *pk.m1(cpos), *pk.m1(sizes))
-    return _finish_sparse_out(lib, handle, A.nrows, B.ncols, cpos, sizes)
+    C = _finish_sparse_out(lib, handle, A.nrows, B.ncols, cpos, sizes)
+    if sharded:
+        C.entry_offset, C.total_nnz = int(sizes[11]), int(sizes[12])
+    return C
 
 
 def elews_csr_csr(A, B):
@@ -304,13 +315,13 @@ def elews_csr_csr(A, B):
     return _finish_sparse_out(lib, handle, A.nrows, A.ncols, cpos, sizes)
 
 
-def masked_pair_count(A, B, M):
-    """SUM(C<M,push> = A @ B) under plus-pair as an exact integer."""
+def masked_pair_count(A, B, M, sharded=False):
+    """SUM(C<M,push> = A @ B) under plus-pair as an exact integer (with ``sharded``: over all ranks' blocks)."""
     A, B, M = as_sparse(A), as_sparse(B), as_sparse(M)
     lib = _lib.load()
     pk = _Packer()
     out = np.zeros(1, dtype=np.int64)
-    fn, _, (A, B, M) = _entry(lib, "masked_spgemm_count", A, B, M)
+    fn, _, (A, B, M) = _entry(lib, _name("masked_spgemm_count", sharded), A, B, M)
     fn(*pk.sparse(A), *pk.sparse(B), *pk.sparse(M), MASK_PUSH, PLUS_PAIR, *pk.m1(out))
     _lib.check()
     return int(out[0])

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "comm.cuh"
 
 extern "C" {
 // device-pointer layer (declared in include/comet_b200.h)
@@ -161,12 +162,28 @@ struct DevBag {
         if (bytes) CB_CUDA(cudaMemcpyAsync(*p, host, bytes, cudaMemcpyHostToDevice, st));
         return 0;
     }
-    // n indices of isz bytes -> int64 on the device (int32 input is widened there, not on the host)
-    int upload_idx(int64_t **p, const void *host, int64_t n, int isz)
+    // An array every rank needs whole (the replicated operand of a sharded call): without a
+    // communicator it is uploaded as it is; with one, this rank uploads slice number `rank` of it and
+    // the slices are exchanged between the GPUs, so each PCIe link carries one N-th of the bytes.
+    // Every rank must pass the same host contents.
+    int upload_rep(void **p, const void *host, size_t bytes, Comm *cm)
     {
-        if (isz == 8) return upload((void **)p, host, (size_t)n * 8);
+        if (!cm || cm->nranks == 1) return upload(p, host, bytes);
+        const size_t s = comm_slice_bytes(bytes, cm->nranks);
+        CB_TRY(alloc(p, s * (size_t)cm->nranks));
+        const size_t lo = s * (size_t)cm->rank;
+        if (lo < bytes) {
+            const size_t n = bytes - lo < s ? bytes - lo : s;
+            CB_CUDA(cudaMemcpyAsync((char *)*p + lo, (const char *)host + lo, n, cudaMemcpyHostToDevice, st));
+        }
+        return comm_allgather_inplace(cm, *p, s, st);
+    }
+    // n indices of isz bytes -> int64 on the device (int32 input is widened there, not on the host)
+    int upload_idx(int64_t **p, const void *host, int64_t n, int isz, Comm *cm = nullptr)
+    {
+        if (isz == 8) return upload_rep((void **)p, host, (size_t)n * 8, cm);
         void *narrow = nullptr;
-        CB_TRY(upload(&narrow, host, (size_t)n * 4));
+        CB_TRY(upload_rep(&narrow, host, (size_t)n * 4, cm));
         CB_TRY(alloc((void **)p, (size_t)n * 8));
         return widen_i32_to_i64((const int32_t *)narrow, *p, n, st);
     }
@@ -194,36 +211,61 @@ static int pool_keep()
     return 0;
 }
 
-// Uploads a sparse operand; for COO it also derives the row pointer on the device.
+// Uploads a sparse operand; for COO it also derives the row pointer on the device.  The column
+// coordinates (and DCSR's row coordinates) are range-checked on the device and the stream is
+// synchronised, so a coordinate outside the matrix is reported here, before any kernel that gathers
+// through it has been launched.
 static int upload_sparse(const char *what, const HostSparse &h, DevBag &bag, DevSparse *d,
-                         bool need_val = true)
+                         bool need_val = true, Comm *rep = nullptr)
 {
     memset(d, 0, sizeof(*d));
     cudaStream_t st = bag.st;
-    CB_TRY(bag.upload_idx(&d->crd, h.a2crd, h.nnz, h.isz));
-    if (need_val) CB_TRY(bag.upload((void **)&d->val, h.val, (size_t)h.nnz * 8));
+    CB_TRY(bag.upload_idx(&d->crd, h.a2crd, h.nnz, h.isz, rep));
+    if (need_val) CB_TRY(bag.upload_rep((void **)&d->val, h.val, (size_t)h.nnz * 8, rep));
+    int *flags = nullptr;                     // [0] coordinates in range, [1] COO rows ascending and in range
+    CB_TRY(bag.alloc((void **)&flags, 2 * sizeof(int)));
+    int got[2] = {1, 1};
+    CB_CUDA(cudaMemcpyAsync(flags, got, sizeof(got), cudaMemcpyHostToDevice, st));
+    CB_TRY(check_index_range(d->crd, h.nnz, h.ncols, flags, st));
     if (h.fmt == F_CSR) {
         d->nrows_k = h.nrows;
-        CB_TRY(bag.upload_idx(&d->pos, h.a2pos, h.nrows + 1, h.isz));
+        CB_TRY(bag.upload_idx(&d->pos, h.a2pos, h.nrows + 1, h.isz, rep));
     } else if (h.fmt == F_DCSR) {
         d->nrows_k = h.nstored;
-        CB_TRY(bag.upload_idx(&d->pos, h.a2pos, h.nstored + 1, h.isz));
-        CB_TRY(bag.upload_idx(&d->row_ids, h.a1crd, h.nstored, h.isz));
+        CB_TRY(bag.upload_idx(&d->pos, h.a2pos, h.nstored + 1, h.isz, rep));
+        CB_TRY(bag.upload_idx(&d->row_ids, h.a1crd, h.nstored, h.isz, rep));
+        CB_TRY(check_index_range(d->row_ids, h.nstored, h.nrows, flags, st));
     } else {
         d->nrows_k = h.nrows;
-        CB_TRY(bag.upload_idx(&d->rows, h.a1crd, h.nnz, h.isz));
+        CB_TRY(bag.upload_idx(&d->rows, h.a1crd, h.nnz, h.isz, rep));
         CB_TRY(bag.alloc((void **)&d->pos, (size_t)(h.nrows + 1) * 8));
-        int *flag = nullptr;
-        CB_TRY(bag.alloc((void **)&flag, sizeof(int)));
-        int one = 1, got = 1;
-        CB_CUDA(cudaMemcpyAsync(flag, &one, sizeof(int), cudaMemcpyHostToDevice, st));
-        CB_TRY(coo_rows_to_pos(d->rows, h.nnz, h.nrows, d->pos, flag, st));
-        CB_CUDA(cudaMemcpyAsync(&got, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
-        CB_CUDA(cudaStreamSynchronize(st));
-        if (!got)
-            return fail("%s: COO row coordinates must be ascending and inside [0, rows) "
-                        "(the order the reference reader produces)", what);
+        CB_TRY(coo_rows_to_pos(d->rows, h.nnz, h.nrows, d->pos, flags + 1, st));
     }
+    CB_CUDA(cudaMemcpyAsync(got, flags, sizeof(got), cudaMemcpyDeviceToHost, st));
+    CB_CUDA(cudaStreamSynchronize(st));
+    if (!got[1])
+        return fail("%s: COO row coordinates must be ascending and inside [0, rows) "
+                    "(the order the reference reader produces)", what);
+    if (!got[0])
+        return fail("%s: a coordinate lies outside the matrix (crd must be in [0, %lld)%s)", what,
+                    (long long)h.ncols, h.fmt == F_DCSR ? ", stored row coordinates in [0, rows)" : "");
+    return 0;
+}
+
+// Range check (then a stream synchronisation) of coordinate arrays uploaded outside upload_sparse:
+// cols in [0, ncols), rows (COO row coordinates or DCSR stored-row coordinates, may be null) in [0, nrows).
+static int verify_coords(const char *what, DevBag &bag, const int64_t *cols, int64_t ncoords, int64_t ncols,
+                         const int64_t *rows, int64_t nrowcoords, int64_t nrows)
+{
+    int *flag = nullptr;
+    CB_TRY(bag.alloc((void **)&flag, sizeof(int)));
+    int got = 1;
+    CB_CUDA(cudaMemcpyAsync(flag, &got, sizeof(int), cudaMemcpyHostToDevice, bag.st));
+    CB_TRY(check_index_range(cols, ncoords, ncols, flag, bag.st));
+    if (rows) CB_TRY(check_index_range(rows, nrowcoords, nrows, flag, bag.st));
+    CB_CUDA(cudaMemcpyAsync(&got, flag, sizeof(int), cudaMemcpyDeviceToHost, bag.st));
+    CB_CUDA(cudaStreamSynchronize(bag.st));
+    if (!got) return fail("%s: a coordinate lies outside the %lld x %lld matrix", what, (long long)nrows, (long long)ncols);
     return 0;
 }
 
@@ -262,6 +304,38 @@ static void fill_sizes(void *sizes_ptr, int64_t sizes_rank, int64_t nrows, int64
     for (int i = 0; i < 11 && i < s.n; i++) ((int64_t *)s.data)[i] = v[i];
 }
 
+// Sharded calls are collective: every rank of the communicator makes the same call.  A rank that finds
+// a fault in its own operands must not simply return, or the others would wait for it in the next
+// exchange.  So after the local checks the ranks agree on a status (an all-reduce of one integer);
+// a rank that leaves early takes part from the destructor with a failure, and everybody returns.
+struct ShardGuard {
+    Comm *cm;
+    cudaStream_t st;
+    bool agreed;
+    ShardGuard(Comm *c, cudaStream_t s) : cm(c), st(s), agreed(c == nullptr || c->nranks == 1) {}
+    ~ShardGuard() { if (!agreed) exchange(1); }
+    int exchange(int mine)
+    {
+        agreed = true;
+        int64_t *d = nullptr, h = mine ? 1 : 0;
+        if (cudaMallocAsync((void **)&d, 8, st) != cudaSuccess) return 1;
+        cudaMemcpyAsync(d, &h, 8, cudaMemcpyHostToDevice, st);
+        comm_allreduce_sum_i64(cm, d, 1, st);
+        cudaMemcpyAsync(&h, d, 8, cudaMemcpyDeviceToHost, st);
+        cudaStreamSynchronize(st);
+        cudaFreeAsync(d, st);
+        return h != 0;
+    }
+    // rc: this rank's status so far.  Returns non-zero if any rank failed.
+    int agree(int rc)
+    {
+        if (agreed) return rc;
+        const int any = exchange(rc);
+        if (any && !rc) return fail("sharded call: another rank reported an error in its operands");
+        return rc;
+    }
+};
+
 static int spmv_host(const HostSparse &A, Arr x, Arr y, int semiring, int accumulate)
 {
     if (x.n < A.ncols) return fail("spmv: x shorter than the column count");
@@ -287,16 +361,22 @@ static int spmv_host(const HostSparse &A, Arr x, Arr y, int semiring, int accumu
 // directions can run at the same time if the work is cut into column panels: panel j of B is
 // uploaded while panel j-1 is multiplied and panel j-2 of C is downloaded (strided 2-D copies
 // between the row-major host matrices and packed panels on the device, two buffers each).
+// With a communicator, a rank uploads only its N-th of the rows of each panel of B and the panel is
+// completed by an all-gather on the compute stream before the kernel that reads it.
 static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &bag, const Mat &B, const Mat &C,
-                            int semiring, int64_t panel, cudaStream_t st)
+                            int semiring, int64_t panel, cudaStream_t st, Comm *cm)
 {
     cudaStream_t up = aux_stream(0), down = aux_stream(1);
     if (!up || !down) return fail("spmm: could not create the copy streams");
     const int64_t k = B.cols;
+    const int nranks = cm ? cm->nranks : 1, rank = cm ? cm->rank : 0;
+    const int64_t slice_rows = ceil_div(A.ncols, nranks);           // rows of B this rank uploads
+    const int64_t my_lo = slice_rows * rank < A.ncols ? slice_rows * rank : A.ncols;
+    const int64_t my_rows = A.ncols - my_lo < slice_rows ? A.ncols - my_lo : slice_rows;
     double *dB[2], *dC[2];
     cudaEvent_t in[2], comp[2], out[2];
     for (int i = 0; i < 2; i++) {
-        CB_TRY(bag.alloc((void **)&dB[i], (size_t)A.ncols * panel * 8));
+        CB_TRY(bag.alloc((void **)&dB[i], (size_t)slice_rows * nranks * panel * 8));
         CB_TRY(bag.alloc((void **)&dC[i], (size_t)A.nrows * panel * 8));
         CB_CUDA(cudaEventCreateWithFlags(&in[i], cudaEventDisableTiming));
         CB_CUDA(cudaEventCreateWithFlags(&comp[i], cudaEventDisableTiming));
@@ -313,10 +393,15 @@ static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &ba
         const int b = (int)(j & 1);
         const int64_t w = (k - c0) < panel ? (k - c0) : panel;
         if (j >= 2) CB_CUDA(cudaStreamWaitEvent(up, comp[b], 0));       // panel j-2 no longer reads dB[b]
-        CB_CUDA(cudaMemcpy2DAsync(dB[b], (size_t)panel * 8, B.data + c0, (size_t)B.s0 * 8, (size_t)w * 8,
-                                  (size_t)A.ncols, cudaMemcpyHostToDevice, up));
+        if (my_rows > 0)
+            CB_CUDA(cudaMemcpy2DAsync(dB[b] + my_lo * panel, (size_t)panel * 8, B.data + my_lo * B.s0 + c0,
+                                      (size_t)B.s0 * 8, (size_t)w * 8, (size_t)my_rows, cudaMemcpyHostToDevice, up));
         CB_CUDA(cudaEventRecord(in[b], up));
         CB_CUDA(cudaStreamWaitEvent(st, in[b], 0));
+        if (nranks > 1) {
+            rc = comm_allgather_inplace(cm, dB[b], (size_t)slice_rows * panel * 8, st);
+            if (rc) break;
+        }
         if (j >= 2) CB_CUDA(cudaStreamWaitEvent(st, out[b], 0));        // panel j-2 has left dC[b]
         rc = comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, w, dA.row_ids, dA.pos, dA.crd, dA.val, dB[b],
                                          panel, dC[b], panel, semiring, 0, 0, st);
@@ -335,17 +420,26 @@ static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &ba
     return 0;
 }
 
-static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiring, int accumulate)
+static int spmm_check(const HostSparse &A, const Mat &B, const Mat &C)
 {
     if (B.rows < A.ncols) return fail("spmm: B has fewer rows than A has columns");
     if (C.rows < A.nrows || C.cols != B.cols) return fail("spmm: C has the wrong shape");
     if ((B.cols > 1 && B.s1 != 1) || (C.cols > 1 && C.s1 != 1) || B.s0 < B.cols || C.s0 < C.cols)
         return fail("spmm: B and C must be row-major");
+    return 0;
+}
+
+// cm != null: A and C are this rank's row block, B is the whole (replicated) dense operand.
+static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiring, int accumulate, Comm *cm)
+{
     cudaStream_t st;
     CB_TRY(need_stream(&st));
+    ShardGuard guard(cm, st);
     DevBag bag(st);
     DevSparse dA;
-    CB_TRY(upload_sparse("spmm", A, bag, &dA));
+    int rc = spmm_check(A, B, C);
+    if (!rc) rc = upload_sparse("spmm", A, bag, &dA);
+    CB_TRY(guard.agree(rc));
     const int64_t k = B.cols;
     {
         // panels of 32 columns (256-byte rows) once the dense operands are big enough to matter
@@ -355,13 +449,15 @@ static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiri
         double min_bytes = 256e6;
         const char *menv = getenv("COMET_B200_SPMM_PANEL_MIN_BYTES");
         if (menv) min_bytes = atof(menv);
-        const bool big = (double)(A.ncols + A.nrows) * (double)k * 8.0 >= min_bytes;
+        // (decided from B alone: under a communicator every rank must take the same branch, and the
+        // blocks of A differ from rank to rank)
+        const bool big = (double)A.ncols * (double)k * 8.0 * 2.0 >= min_bytes;
         if (!accumulate && A.fmt != F_DCSR && panel >= 2 && panel % 2 == 0 && k >= 2 * panel && big &&
             semiring == COMET_B200_PLUS_TIMES)
-            return spmm_host_panels(A, dA, bag, B, C, semiring, panel, st);
+            return spmm_host_panels(A, dA, bag, B, C, semiring, panel, st, cm);
     }
     double *dB, *dC;
-    CB_TRY(bag.upload((void **)&dB, B.data, (size_t)((A.ncols - 1) * B.s0 + k) * 8 * (A.ncols > 0)));
+    CB_TRY(bag.upload_rep((void **)&dB, B.data, (size_t)((A.ncols - 1) * B.s0 + k) * 8 * (A.ncols > 0), cm));
     size_t cbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * C.s0 + k) * 8 : 0;
     bool keep_old = accumulate || A.fmt == F_DCSR || C.s0 != k;
     if (keep_old) CB_TRY(bag.upload((void **)&dC, C.data, cbytes));
@@ -407,6 +503,19 @@ using namespace cb200;
     (void)P##1tile_pos_ptr; (void)P##1tile_crd_rank; (void)P##1tile_crd_ptr; (void)P##2tile_pos_rank; \
     (void)P##2tile_pos_ptr; (void)P##2tile_crd_rank; (void)P##2tile_crd_ptr
 
+// First argument of the *_impl functions below: bytes per index (8 or 4), plus MODE_SHARDED for the
+// entry points that run under the device's communicator.
+enum { MODE_SHARDED = 16 };
+
+static int mode_comm(int mode, Comm **cm)
+{
+    *cm = nullptr;
+    if (!(mode & MODE_SHARDED)) return 0;
+    *cm = comm_current();
+    if (!*cm) return fail("sharded call: this device has no communicator (comet_b200_comm_init comes first)");
+    return 0;
+}
+
 static void spmv_impl(int isz, COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr, int64_t y_rank,
                       void *y_ptr, int32_t semiring, int32_t accumulate)
 {
@@ -419,52 +528,70 @@ static void spmv_impl(int isz, COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_p
     spmv_host(A, x, y, semiring, accumulate);
 }
 
-static void spmm_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank,
+static void spmm_impl(int mode, COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank,
                       void *C_ptr, int32_t semiring, int32_t accumulate)
 {
     UNUSED_TILES(A);
     clear_error();
+    const int isz = mode & 15;
+    Comm *cm;
+    if (mode_comm(mode, &cm)) return;
     HostSparse A;
     Mat B, C;
-    if (GET_SPARSE("spmm: A", A, &A)) return;
-    if (get2d("spmm: B", B_rank, B_ptr, &B) || get2d("spmm: C", C_rank, C_ptr, &C)) return;
-    spmm_host(A, B, C, semiring, accumulate);
+    int rc = GET_SPARSE("spmm: A", A, &A) || get2d("spmm: B", B_rank, B_ptr, &B) || get2d("spmm: C", C_rank, C_ptr, &C);
+    if (rc) {
+        if (cm) { cudaStream_t st; if (!need_stream(&st)) ShardGuard(cm, st).agree(1); }
+        return;
+    }
+    spmm_host(A, B, C, semiring, accumulate, cm);
 }
 
-static void sddmm_impl(int isz, COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank,
+static int sddmm_check(const HostSparse &S, const HostSparse &O, const Mat &X, const Mat &D)
+{
+    if (S.fmt != F_CSR || O.fmt != F_CSR) return fail("sddmm: S and O must be CSR");
+    const int64_t k = X.cols;
+    if (X.rows < S.nrows || (k > 1 && X.s1 != 1) || X.s0 < k) return fail("sddmm: X must be row-major [rows, K]");
+    if (D.rows != k || D.cols < S.ncols) return fail("sddmm: D must have sizes {K, cols}");
+    if (!((D.s0 == 1 && D.s1 >= k) || (D.s1 == 1 && D.s0 >= D.cols)))
+        return fail("sddmm: D must be contiguous along one of its dimensions");
+    return 0;
+}
+
+// Sharded: S, X and O are this rank's row block; D (all of Y) is the replicated operand.
+static void sddmm_impl(int mode, COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank,
                        void *D_ptr, COMET_B200_SPARSE2D(O))
 {
     UNUSED_TILES(S);
     UNUSED_TILES(O);
     clear_error();
-    HostSparse S, O;
-    Mat X, D;
-    if (GET_SPARSE("sddmm: S", S, &S) || GET_SPARSE("sddmm: O", O, &O)) return;
-    if (get2d("sddmm: X", X_rank, X_ptr, &X) || get2d("sddmm: D", D_rank, D_ptr, &D)) return;
-    if (S.fmt != F_CSR || O.fmt != F_CSR) { fail("sddmm: S and O must be CSR"); return; }
-    const int64_t k = X.cols;
-    if (X.rows < S.nrows || (k > 1 && X.s1 != 1) || X.s0 < k) { fail("sddmm: X must be row-major [rows, K]"); return; }
-    if (D.rows != k || D.cols < S.ncols) { fail("sddmm: D must have sizes {K, cols}"); return; }
+    const int isz = mode & 15;
+    Comm *cm;
+    if (mode_comm(mode, &cm)) return;
     cudaStream_t st;
     if (need_stream(&st)) return;
+    ShardGuard guard(cm, st);
+    HostSparse S, O;
+    Mat X, D;
     DevBag bag(st);
     DevSparse dS;
-    if (upload_sparse("sddmm", S, bag, &dS)) return;
-    double *dX, *dY, *dOut;
-    if (bag.upload((void **)&dX, X.data, S.nrows > 0 ? (size_t)((S.nrows - 1) * X.s0 + k) * 8 : 0)) return;
+    double *dX = nullptr, *dY = nullptr, *dOut = nullptr;
+    int rc = GET_SPARSE("sddmm: S", S, &S) || GET_SPARSE("sddmm: O", O, &O) ||
+             get2d("sddmm: X", X_rank, X_ptr, &X) || get2d("sddmm: D", D_rank, D_ptr, &D);
+    if (!rc) rc = sddmm_check(S, O, X, D);
+    if (!rc) rc = upload_sparse("sddmm", S, bag, &dS);
+    const int64_t k = rc ? 0 : X.cols;
+    if (!rc) rc = bag.upload((void **)&dX, X.data, S.nrows > 0 ? (size_t)((S.nrows - 1) * X.s0 + k) * 8 : 0);
+    if (guard.agree(rc)) return;
     int64_t ldy;
-    if (D.s0 == 1 && D.s1 >= k) {            // a row-major [cols, K] matrix viewed transposed
+    if (D.s0 == 1) {                          // a row-major [cols, K] matrix viewed transposed
         ldy = D.s1;
-        if (bag.upload((void **)&dY, D.data, S.ncols > 0 ? (size_t)((S.ncols - 1) * ldy + k) * 8 : 0)) return;
-    } else if (D.s1 == 1 && D.s0 >= D.cols) {   // D[k, j]: transpose on the device
+        if (bag.upload_rep((void **)&dY, D.data, S.ncols > 0 ? (size_t)((S.ncols - 1) * ldy + k) * 8 : 0, cm)) return;
+    } else {                                  // D[k, j]: transpose on the device
         double *dD;
-        if (bag.upload((void **)&dD, D.data, k > 0 ? (size_t)((k - 1) * D.s0 + S.ncols) * 8 : 0)) return;
+        if (bag.upload_rep((void **)&dD, D.data, k > 0 ? (size_t)((k - 1) * D.s0 + S.ncols) * 8 : 0, cm)) return;
         ldy = k + (k & 1);
         if (bag.alloc((void **)&dY, (size_t)S.ncols * ldy * 8)) return;
         if (comet_b200_dev_transpose_f64(k, S.ncols, dD, D.s0, dY, ldy, st)) return;
-    } else {
-        fail("sddmm: D must be contiguous along one of its dimensions");
-        return;
     }
     if (bag.alloc((void **)&dOut, (size_t)S.nnz * 8)) return;
     if (comet_b200_dev_sddmm_f64_i64(S.nrows, S.nnz, k, dS.pos, dS.crd, dS.val, dX, X.s0, dY, ldy, dOut, st))
@@ -498,6 +625,7 @@ static void elews_sd_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void 
     if (bag.upload((void **)&dA.val, A.val, (size_t)A.nnz * 8)) return;
     if (A.fmt == F_CSR) { if (bag.upload_idx(&dA.pos, A.a2pos, A.nrows + 1, A.isz)) return; }
     else { if (bag.upload_idx(&dA.rows, A.a1crd, A.nnz, A.isz)) return; }
+    if (verify_coords("elews_mul: A", bag, dA.crd, A.nnz, A.ncols, dA.rows, A.nnz, A.nrows)) return;
     double *dB, *dOut;
     if (bag.upload((void **)&dB, B.data, A.nrows > 0 ? (size_t)((A.nrows - 1) * B.s0 + A.ncols) * 8 : 0)) return;
     if (bag.alloc((void **)&dOut, (size_t)A.nnz * 8)) return;
@@ -541,6 +669,9 @@ static void elews_to_dense_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank,
         if (bag.upload_idx(&dA.pos, A.a2pos, nstored + 1, A.isz)) return;
         if (A.fmt == F_DCSR && bag.upload_idx(&dA.row_ids, A.a1crd, nstored, A.isz)) return;
     }
+    if (verify_coords("elews_mul: A", bag, dA.crd, A.nnz, A.ncols, A.fmt == F_COO ? dA.rows : dA.row_ids,
+                      A.fmt == F_COO ? A.nnz : nstored, A.nrows))
+        return;
     double *dB, *dC;
     const size_t bbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * B.s0 + A.ncols) * 8 : 0;
     const size_t cbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * C.s0 + A.ncols) * 8 : 0;
@@ -629,6 +760,7 @@ static void transpose_impl(int isz, int32_t A1format, int32_t A2format, int64_t 
     if (a_csr) {
         int64_t *dpos = nullptr;
         if (bag.upload_idx(&dpos, a2pos.data, nrows + 1, isz) || bag.alloc((void **)&omaj, (size_t)(ncols + 1) * 8)) return;
+        if (verify_coords("transpose: A", bag, dcrd, nnz, ncols, nullptr, 0, nrows)) return;
         if (comet_b200_dev_csr_transpose_f64_i64(nrows, ncols, nnz, dpos, dcrd, dval, omaj, ocrd, oval, st)) return;
         if (download_idx(bag, omaj, (char *)b2pos.data, ncols + 1, isz, st)) return;
         if (b1pos.data && b1pos.n >= 1) idx_set((char *)b1pos.data, 0, isz, ncols);
@@ -697,29 +829,36 @@ static void dense_sparse_impl(int isz, int64_t A_rank, void *A_ptr, COMET_B200_S
     finish(st);
 }
 
+// cm != null (sharded): A, M and the output are this rank's row block, B is the replicated operand.
 static int64_t sparse_out_symbolic(int isz, int kind, const HostSparse &A, const HostSparse &B,
                                    const HostSparse *M, int semiring, Arr cpos, int64_t sizes_rank,
-                                   void *sizes_ptr)
+                                   void *sizes_ptr, Comm *cm = nullptr)
 {
-    if (A.fmt != F_CSR || B.fmt != F_CSR || (M && M->fmt != F_CSR))
-        return fail("sparse output: operands must be CSR (COMET's workspace transformation handles CSR only)"), 0;
-    if (cpos.n < A.nrows + 1) return fail("sparse output: C2pos shorter than rows+1"), 0;
-    if (kind == 0 && B.nrows < A.ncols) return fail("spgemm: B has fewer rows than A has columns"), 0;
-    if (kind == 1 && (B.nrows != A.nrows)) return fail("elews_mul: row counts differ"), 0;
     cudaStream_t st;
     if (need_stream(&st)) return 0;
+    ShardGuard guard(cm, st);
     DevBag bag(st);
     DevSparse dA, dB, dM;
     memset(&dM, 0, sizeof(dM));
-    if (upload_sparse("A", A, bag, &dA)) return 0;
-    bool same = B.a2pos == A.a2pos && B.a2crd == A.a2crd && B.val == A.val;
-    if (same) dB = dA;
-    else if (upload_sparse("B", B, bag, &dB)) return 0;
-    if (M) {
+    int rc0 = 0;
+    if (A.fmt != F_CSR || B.fmt != F_CSR || (M && M->fmt != F_CSR))
+        rc0 = fail("sparse output: operands must be CSR (COMET's workspace transformation handles CSR only)");
+    else if (cpos.n < A.nrows + 1) rc0 = fail("sparse output: C2pos shorter than rows+1");
+    else if (kind == 0 && B.nrows < A.ncols) rc0 = fail("spgemm: B has fewer rows than A has columns");
+    else if (kind == 1 && (B.nrows != A.nrows)) rc0 = fail("elews_mul: row counts differ");
+    else if (M && M->nrows < A.nrows) rc0 = fail("spgemm: the mask has fewer rows than A");
+    const bool sharded = cm && cm->nranks > 1;
+    const bool same = !sharded && B.a2pos == A.a2pos && B.a2crd == A.a2crd && B.val == A.val;
+    if (!rc0) rc0 = upload_sparse("A", A, bag, &dA);
+    if (!rc0 && M) {
         if (M->a2pos == A.a2pos && M->a2crd == A.a2crd) dM = dA;
-        else if (M->a2pos == B.a2pos && M->a2crd == B.a2crd) dM = dB;
-        else if (upload_sparse("M", *M, bag, &dM, false)) return 0;
+        else if (!sharded && !same && M->a2pos == B.a2pos && M->a2crd == B.a2crd) dM.pos = nullptr;   // set below
+        else rc0 = upload_sparse("M", *M, bag, &dM, false);
     }
+    if (guard.agree(rc0)) return 0;
+    if (same) dB = dA;
+    else if (upload_sparse("B", B, bag, &dB, true, cm)) return 0;
+    if (M && !dM.pos && M->a2pos == B.a2pos && M->a2crd == B.a2crd) dM = dB;
     int64_t *dcpos;
     if (bag.alloc((void **)&dcpos, (size_t)(A.nrows + 1) * 8)) return 0;
     int64_t nnz = 0, dev_handle = 0;
@@ -752,6 +891,26 @@ static int64_t sparse_out_symbolic(int isz, int kind, const HostSparse &A, const
         return fail("sparse output: copy of C2pos failed"), 0;
     }
     fill_sizes(sizes_ptr, sizes_rank, A.nrows, kind == 0 ? B.ncols : A.ncols, nnz);
+    if (cm) {
+        // position of this block in the whole result: entries [11] and [12] of the sizes memref (when it has
+        // them) receive the number of entries the lower ranks' blocks hold and the total over all ranks
+        int64_t *dnnz = nullptr, *dall = nullptr;
+        std::vector<int64_t> all((size_t)cm->nranks, 0);
+        if (bag.upload((void **)&dnnz, &nnz, 8) || bag.alloc((void **)&dall, (size_t)cm->nranks * 8) ||
+            comm_allgather_i64(cm, dnnz, dall, st) ||
+            cudaMemcpyAsync(all.data(), dall, (size_t)cm->nranks * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+            cudaStreamSynchronize(st) != cudaSuccess) {
+            comet_b200_handle_destroy(dev_handle);
+            return fail("sparse output: exchange of the per-rank entry counts failed"), 0;
+        }
+        int64_t before = 0, total = 0;
+        for (int r = 0; r < cm->nranks; r++) { if (r < cm->rank) before += all[r]; total += all[r]; }
+        Arr sz;
+        if (get1d("sizes", sizes_rank, sizes_ptr, 8, &sz) == 0 && sz.data && sz.n >= 13) {
+            ((int64_t *)sz.data)[11] = before;
+            ((int64_t *)sz.data)[12] = total;
+        }
+    }
     HostPlan *hp = new HostPlan();
     hp->dev_handle = dev_handle;
     hp->nnz = nnz;
@@ -762,7 +921,7 @@ static int64_t sparse_out_symbolic(int isz, int kind, const HostSparse &A, const
     return dev_handle;
 }
 
-static int64_t spgemm_symbolic_impl(int isz, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
+static int64_t spgemm_symbolic_impl(int mode, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
                                     COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
                                     int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank,
                                     void *sizes_ptr)
@@ -771,17 +930,22 @@ static int64_t spgemm_symbolic_impl(int isz, COMET_B200_SPARSE2D(A), COMET_B200_
     UNUSED_TILES(B);
     UNUSED_TILES(M);
     clear_error();
+    const int isz = mode & 15;
+    Comm *cm;
+    if (mode_comm(mode, &cm)) return 0;
     HostSparse A, B, M;
     Arr cpos;
-    if (GET_SPARSE("spgemm: A", A, &A) || GET_SPARSE("spgemm: B", B, &B)) return 0;
-    if (mask_type != COMET_B200_MASK_NONE && mask_type != COMET_B200_MASK_PUSH) {
-        fail("spgemm: unsupported mask type %d (none and push are handled)", mask_type);
+    const bool masked = mask_type == COMET_B200_MASK_PUSH;
+    int rc = GET_SPARSE("spgemm: A", A, &A) || GET_SPARSE("spgemm: B", B, &B);
+    if (!rc && mask_type != COMET_B200_MASK_NONE && mask_type != COMET_B200_MASK_PUSH)
+        rc = fail("spgemm: unsupported mask type %d (none and push are handled)", mask_type);
+    if (!rc && masked) rc = GET_SPARSE("spgemm: M", M, &M);
+    if (!rc) rc = get1d("spgemm: C2pos", C2pos_rank, C2pos_ptr, isz, &cpos);
+    if (rc) {
+        if (cm) { cudaStream_t st; if (!need_stream(&st)) ShardGuard(cm, st).agree(1); }
         return 0;
     }
-    bool masked = mask_type == COMET_B200_MASK_PUSH;
-    if (masked && GET_SPARSE("spgemm: M", M, &M)) return 0;
-    if (get1d("spgemm: C2pos", C2pos_rank, C2pos_ptr, isz, &cpos)) return 0;
-    return sparse_out_symbolic(isz, 0, A, B, masked ? &M : nullptr, semiring, cpos, sizes_rank, sizes_ptr);
+    return sparse_out_symbolic(isz, 0, A, B, masked ? &M : nullptr, semiring, cpos, sizes_rank, sizes_ptr, cm);
 }
 
 static int64_t elews_ss_symbolic_impl(int isz, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
@@ -842,41 +1006,54 @@ static void spgemm_numeric_impl(int isz, int64_t handle, int64_t C2crd_rank, voi
     delete hp;
 }
 
-static void masked_count_impl(int isz, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
-                              COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
-                              int64_t out_rank, void *out_ptr)
+// Sharded: A and M are this rank's row block, B the replicated operand; out[0] receives the count over
+// ALL ranks' blocks (an all-reduce on the stream of the counting kernels).
+static void masked_count_impl(int mode, COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B),
+                              COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring, int64_t out_rank,
+                              void *out_ptr)
 {
     UNUSED_TILES(A);
     UNUSED_TILES(B);
     UNUSED_TILES(M);
     clear_error();
-    HostSparse A, B, M;
-    Arr out;
-    if (GET_SPARSE("masked count: A", A, &A) || GET_SPARSE("masked count: B", B, &B) ||
-        GET_SPARSE("masked count: M", M, &M))
-        return;
-    if (get1d("masked count: out", out_rank, out_ptr, 8, &out) || out.n < 1) { fail("masked count: out must hold one int64"); return; }
-    if (mask_type != COMET_B200_MASK_PUSH || semiring != COMET_B200_PLUS_PAIR) {
-        fail("masked count: only the push mask with the plus-pair semiring is handled");
-        return;
-    }
-    if (A.fmt != F_CSR || B.fmt != F_CSR || M.fmt != F_CSR) { fail("masked count: operands must be CSR"); return; }
-    if (B.nrows < A.ncols || M.nrows < A.nrows) { fail("masked count: shapes do not match"); return; }
+    const int isz = mode & 15;
+    Comm *cm;
+    if (mode_comm(mode, &cm)) return;
     cudaStream_t st;
     if (need_stream(&st)) return;
+    ShardGuard guard(cm, st);
+    HostSparse A, B, M;
+    Arr out;
     DevBag bag(st);
     DevSparse dA, dB, dM;
-    if (upload_sparse("A", A, bag, &dA, false)) return;
-    if (B.a2pos == A.a2pos && B.a2crd == A.a2crd) dB = dA;
-    else if (upload_sparse("B", B, bag, &dB, false)) return;
-    if (M.a2pos == A.a2pos && M.a2crd == A.a2crd) dM = dA;
-    else if (M.a2pos == B.a2pos && M.a2crd == B.a2crd) dM = dB;
-    else if (upload_sparse("M", M, bag, &dM, false)) return;
+    memset(&dM, 0, sizeof(dM));
+    int rc = GET_SPARSE("masked count: A", A, &A) || GET_SPARSE("masked count: B", B, &B) ||
+             GET_SPARSE("masked count: M", M, &M);
+    if (!rc && (get1d("masked count: out", out_rank, out_ptr, 8, &out) || out.n < 1))
+        rc = fail("masked count: out must hold one int64");
+    if (!rc && (mask_type != COMET_B200_MASK_PUSH || semiring != COMET_B200_PLUS_PAIR))
+        rc = fail("masked count: only the push mask with the plus-pair semiring is handled");
+    if (!rc && (A.fmt != F_CSR || B.fmt != F_CSR || M.fmt != F_CSR)) rc = fail("masked count: operands must be CSR");
+    if (!rc && (B.nrows < A.ncols || M.nrows < A.nrows)) rc = fail("masked count: shapes do not match");
+    const bool sharded = cm && cm->nranks > 1;
+    const bool b_is_a = !rc && !sharded && B.a2pos == A.a2pos && B.a2crd == A.a2crd;
+    const bool m_is_a = !rc && M.a2pos == A.a2pos && M.a2crd == A.a2crd;
+    const bool m_is_b = !rc && !m_is_a && !sharded && M.a2pos == B.a2pos && M.a2crd == B.a2crd;
+    if (!rc) rc = upload_sparse("A", A, bag, &dA, false);
+    if (!rc) {
+        if (m_is_a) dM = dA;
+        else if (!m_is_b) rc = upload_sparse("M", M, bag, &dM, false);
+    }
+    if (guard.agree(rc)) return;
+    if (b_is_a) dB = dA;
+    else if (upload_sparse("B", B, bag, &dB, false, cm)) return;
+    if (m_is_b) dM = dB;
     int64_t *dcount;
     if (bag.alloc((void **)&dcount, 8)) return;
     if (comet_b200_dev_masked_spgemm_count_f64_i64(0, A.nrows, B.ncols, A.nnz, B.nnz, M.nnz, dA.pos, dA.crd,
                                                    dB.pos, dB.crd, dM.pos, dM.crd, dcount, st))
         return;
+    if (comm_allreduce_sum_i64(cm, dcount, 1, st)) return;
     if (cudaMemcpyAsync(out.data, dcount, 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) { fail("masked count: copy failed"); return; }
     finish(st);
 }
@@ -931,6 +1108,28 @@ BOTH_WIDTHS(void, masked_spgemm_count, masked_count_impl,
             (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
              int64_t out_rank, void *out_ptr),
             FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, out_rank, out_ptr)
+
+// The same operations on one row block per rank, under the communicator of comet_b200_comm_init.
+#define SHARDED_WIDTHS(RET, NAME, IMPL, PARAMS, ...)                                              \
+    RET comet_b200_##NAME##_sharded_f64_i64 PARAMS { return IMPL(8 | MODE_SHARDED, __VA_ARGS__); } \
+    RET comet_b200_##NAME##_sharded_f64_i32 PARAMS { return IMPL(4 | MODE_SHARDED, __VA_ARGS__); }
+
+SHARDED_WIDTHS(void, spmm, spmm_impl,
+               (COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank, void *C_ptr, int32_t semiring,
+                int32_t accumulate),
+               FWD_SPARSE(A), B_rank, B_ptr, C_rank, C_ptr, semiring, accumulate)
+SHARDED_WIDTHS(void, sddmm, sddmm_impl,
+               (COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O)),
+               FWD_SPARSE(S), X_rank, X_ptr, D_rank, D_ptr, FWD_SPARSE(O))
+SHARDED_WIDTHS(int64_t, spgemm_symbolic, spgemm_symbolic_impl,
+               (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
+                int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr),
+               FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, C2pos_rank,
+               C2pos_ptr, sizes_rank, sizes_ptr)
+SHARDED_WIDTHS(void, masked_spgemm_count, masked_count_impl,
+               (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
+                int64_t out_rank, void *out_ptr),
+               FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, out_rank, out_ptr)
 
 }  // extern "C"
 

@@ -74,6 +74,9 @@ int exclusive_scan_i64(const int64_t *in, int64_t *out, int64_t n, cudaStream_t 
 int coo_rows_to_pos(const int64_t *rows, int64_t nnz, int64_t nrows, int64_t *pos, int *flag_dev,
                     cudaStream_t st);
 
+// *flag_dev (preset to 1 by the caller) becomes 0 if some idx[i] is outside [0, limit)
+int check_index_range(const int64_t *idx, int64_t n, int64_t limit, int *flag_dev, cudaStream_t st);
+
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // Work list of long-row chunks shared by the row-parallel kernels (SLOT_WORKLIST):

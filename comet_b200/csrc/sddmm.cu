@@ -1,15 +1,15 @@
 // SDDMM  out[p] = S.val[p] * sum_k X[i,k] * Y[j,k]   for every stored (i,j) of S (CSR).
 //
-// One warp owns a row i (rows are dealt to warps round-robin, so the long rows
-// that sit together in a power-law matrix spread over all SMs).  The warp keeps
-// X[i,:] in registers, split over groups of G lanes (2*NI doubles per lane); it
-// loads 32 column coordinates with one coalesced streaming load and then works
-// on 32/G stored entries at a time: each group gathers its Y[j,:] with 128-bit
-// loads, multiplies, and finishes its dot product with xor-shuffles.  All
-// groups of a warp work on the same row, so lanes never diverge on row length.
-// The 32 results of a batch are scaled by S.val and written with one coalesced
-// store.  Rows longer than LONG_ROW entries are cut into chunks that go to a
-// work list in scratch memory; a second launch hands each chunk to a warp.
+// Two launches share the work by row length.
+//   rows of at most LONG_ROW entries: warps draw blocks of BLOCK_ROWS consecutive rows from a
+//     counter and walk the block's entries as ONE stream, 32 entries per batch; the row of every
+//     entry is found once per batch by a shuffle binary search over the block's row pointers, the
+//     next batch's coordinates are fetched before the current one is worked on, and groups of G
+//     lanes gather X[i,:] and Y[j,:] with 128-bit loads and finish each dot product with
+//     xor-shuffles.  The 32 results of a batch are scaled by S.val and leave in one coalesced store.
+//   longer rows: cut into CHUNK-entry pieces on a work list in scratch memory by the first launch;
+//     the second launch gives every piece to a warp that keeps X[i,:] in registers.  On power-law
+//     matrices this balanced path carries most of the entries.
 //
 // Bound: HBM.  Algorithmic bytes = 8(n+1) + 24 nnz + 8 K (nrows + ncols).
 #include "common.cuh"

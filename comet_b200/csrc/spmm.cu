@@ -149,7 +149,7 @@ spmm_chunks_kernel(const int64_t *__restrict__ row_ids, const int64_t *__restric
     const int lane = threadIdx.x & 31;
     const unsigned gmask = (T == 32) ? 0xffffffffu : (((1u << T) - 1u) << (lane & ~(T - 1)));
     unsigned count = hdr->count;
-    if (count > chunk_cap) count = 0;   // overflow is reported by the host; do not read past the list
+    if (count > chunk_cap) count = 0;   // cannot happen when nnz == pos[nrows] (the list's capacity is a bound for that nnz); never read past the list
     const int64_t total = (int64_t)count * nslices;
     for (int64_t w = blockIdx.x; w < total; w += gridDim.x) {
         const int slice = (int)(w / count);
@@ -300,7 +300,7 @@ int spmm_rows(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_
         CB_LAUNCH_CHECK();
         return 0;
     }
-    // bits 24-25 of the variant pick the path: 0 = by shape, 1 = entry stream with bulk copies, 2 = row panels
+    // bits 24-25 of the variant pick the path: 0 = by shape, 1 = entry stream (rows of B staged in shared memory by cp.async), 2 = row panels
     const int path = (variant >> 24) & 3;
     if (!pair && path != 2 && (path == 1 || spmm_stream_preferred(nrows, nnz, k))) {
         const int took = spmm_stream(nrows, ncols, nnz, k, row_ids, pos, crd, val, b, ldb, c, ldc, accumulate, path == 1, st);

@@ -18,7 +18,9 @@
 //   <= 128 entries   one warp per row
 //   <= 2048 entries  one CTA per row
 //   longer           cut into units of (4096 mask entries) x (2048 entries of A),
-//                    one CTA per unit, so a huge row spreads over many SMs
+//                    one CTA per unit, so a huge row spreads over many SMs; the mask row is
+//                    ascending, and a segment leaves out the coordinate its predecessor ended
+//                    with, so a coordinate stored twice in M still counts once
 // and rows / units are handed out dynamically (one atomic each), because the work
 // per row (sum of the lengths of the B rows it touches) is very uneven.
 // Every element of every touched B row is read (coalesced, 128-bit loads of int32
@@ -120,16 +122,23 @@ __device__ __forceinline__ unsigned tc_probe(const int32_t *tab, bool linear, in
 
 // Clears and fills the set with mask entries [ms, me); `nthreads` threads with index `tid` cooperate
 // (a warp when !block, the whole CTA otherwise; `flag` is a shared-memory word they all see).
+// `skip` (-1 = none) is a coordinate already counted with the segment before this one: the mask row is
+// ascending, so a coordinate stored twice sits at adjacent positions, and when a segment boundary
+// falls between the two copies the later segment must not hold it again (a mask bit counts once).
 // Returns true if the set had to fall back to linear probing.
 template <int LOG2>
 __device__ __forceinline__ bool tc_fill(int32_t *tab, unsigned *flag, const int32_t *__restrict__ mcrd,
-                                        int64_t ms, int64_t me, int tid, int nthreads, bool block)
+                                        int64_t ms, int64_t me, int tid, int nthreads, bool block,
+                                        int32_t skip = -1)
 {
     for (int s = tid; s < (1 << LOG2); s += nthreads) tab[s] = -1;
     if (tid == 0) *flag = 0u;
     if (block) __syncthreads(); else __syncwarp();
     bool ok = true;
-    for (int64_t t = ms + tid; t < me; t += nthreads) ok = tc_cuckoo_insert<LOG2>(tab, mcrd[t]) && ok;
+    for (int64_t t = ms + tid; t < me; t += nthreads) {
+        const int32_t key = mcrd[t];
+        if (key != skip) ok = tc_cuckoo_insert<LOG2>(tab, key) && ok;
+    }
     if (!ok) *flag = 1u;
     if (block) __syncthreads(); else __syncwarp();
     const bool linear = *flag != 0u;
@@ -137,7 +146,10 @@ __device__ __forceinline__ bool tc_fill(int32_t *tab, unsigned *flag, const int3
         if (block) __syncthreads(); else __syncwarp();
         for (int s = tid; s < (1 << LOG2); s += nthreads) tab[s] = -1;
         if (block) __syncthreads(); else __syncwarp();
-        for (int64_t t = ms + tid; t < me; t += nthreads) tc_linear_insert<LOG2>(tab, mcrd[t]);
+        for (int64_t t = ms + tid; t < me; t += nthreads) {
+            const int32_t key = mcrd[t];
+            if (key != skip) tc_linear_insert<LOG2>(tab, key);
+        }
         if (block) __syncthreads(); else __syncwarp();
     }
     return linear;
@@ -342,7 +354,8 @@ tc_block_kernel(TcHeader *hdr, int which, const int32_t *__restrict__ list,
         for (int64_t seg = ms; seg < me; seg += SEG) {
             const int64_t seg_end = seg + SEG < me ? seg + SEG : me;
             if (threadIdx.x == 0) s_batch = 0;
-            const bool linear = tc_fill<LOG2>(tab, &s_flag, mcrd, seg, seg_end, threadIdx.x, THREADS, true);
+            const int32_t skip = seg > mpos[i] ? mcrd[seg - 1] : -1;     // last coordinate of the segment before
+            const bool linear = tc_fill<LOG2>(tab, &s_flag, mcrd, seg, seg_end, threadIdx.x, THREADS, true, skip);
             hits += tc_stream_rows<LOG2>(tab, linear, as, ae, &s_batch, lane, acrd, bpos, bcrd);
             __syncthreads();
         }

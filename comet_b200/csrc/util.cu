@@ -217,6 +217,30 @@ int coo_rows_to_pos(const int64_t *rows, int64_t nnz, int64_t nrows, int64_t *po
 }
 
 // ---------------------------------------------------------------------------
+// Range check of a coordinate array: *flag_dev is set to 0 when some idx[i] lies outside [0, limit).
+// The kernels index dense operands and bitmaps with these coordinates without further checks, so the
+// host entry points run this once per uploaded array and refuse the call before any of them starts.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) index_range_kernel(const int64_t *__restrict__ idx, int64_t n, int64_t limit,
+                                                          int *flag_dev)
+{
+    bool bad = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t v = idx[i];
+        bad |= (v < 0) | (v >= limit);
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) *flag_dev = 0;
+}
+
+int check_index_range(const int64_t *idx, int64_t n, int64_t limit, int *flag_dev, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    index_range_kernel<<<stream_grid(n), 256, 0, st>>>(idx, n, limit, flag_dev);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
 // Tiled transpose of a row-major f64 matrix through shared memory.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) transpose_kernel(int64_t rows, int64_t cols,

@@ -35,9 +35,13 @@ def rmat_edges(scale, edge_factor, seed=0, probs=RMAT_PROBS, chunk=1 << 24):
         for _level in range(scale):
             u = rng.random(m)
             row_bit = u >= a + b                       # quadrants c and d
-            col_bit = ((u >= a) & (u < a + b)) | (u >= a + b + c)   # quadrants b and d
-            r = (r << 1) | row_bit
-            cc = (cc << 1) | col_bit
+            col_bit = u >= a                           # quadrants b and d: [a, a+b) and [a+b+c, 1)
+            col_bit ^= row_bit
+            col_bit |= u >= a + b + c
+            np.left_shift(r, 1, out=r)
+            np.bitwise_or(r, row_bit, out=r)
+            np.left_shift(cc, 1, out=cc)
+            np.bitwise_or(cc, col_bit, out=cc)
         rows[lo:lo + m] = r
         cols[lo:lo + m] = cc
     return rows, cols
@@ -50,16 +54,27 @@ def rmat_csr(scale, edge_factor, seed=0, drop_self_loops=True, symmetrize=False,
     values: 'u0515' -> U(0.5, 1.5), 'ones' -> 1.0."""
     n = 1 << scale
     rows, cols = rmat_edges(scale, edge_factor, seed)
-    if symmetrize:
-        rows, cols = np.concatenate([rows, cols]), np.concatenate([cols, rows])
-    if drop_self_loops:
-        keep = rows != cols
-        rows, cols = rows[keep], cols[keep]
-    if lower_strict:
-        keep = rows > cols
-        rows, cols = rows[keep], cols[keep]
-    keys = np.unique(rows * n + cols)
+    if symmetrize and lower_strict:
+        # the strict lower triangle of the symmetrised graph: every draw off the diagonal, larger end first
+        hi, lo = np.maximum(rows, cols), np.minimum(rows, cols)
+        keep = hi != lo
+        rows, cols = hi[keep], lo[keep]
+        del hi, lo
+    else:
+        if symmetrize:
+            rows, cols = np.concatenate([rows, cols]), np.concatenate([cols, rows])
+        if drop_self_loops:
+            keep = rows != cols
+            rows, cols = rows[keep], cols[keep]
+        if lower_strict:
+            keep = rows > cols
+            rows, cols = rows[keep], cols[keep]
+    # sorted distinct keys (an in-place sort and one comparison pass; np.unique is many times slower here)
+    keys = rows * n + cols
     del rows, cols
+    keys.sort()
+    if keys.shape[0] > 1:
+        keys = keys[np.concatenate(([True], keys[1:] != keys[:-1]))]
     rng = np.random.default_rng(seed + 1)
     vals = np.ones(keys.shape[0]) if values == "ones" else rng.uniform(0.5, 1.5, keys.shape[0])
     return _csr_from_sorted_keys(keys, n, vals)

@@ -10,11 +10,55 @@ single-GPU kernels on its block.  Collectives only assemble results:
 all-gather of dense row blocks, all-gather of per-shard nnz to place sparse
 row blocks, all-reduce of the triangle count.
 """
+import ctypes
+
 import numpy as np
 import torch
 import torch.distributed as dist
 
 from .api import SparseTensor, as_sparse
+
+
+def slice_bytes(total_bytes, nranks):
+    """Bytes of one slice when a replicated array is exchanged between ``nranks`` ranks: the same rule as
+    ``comet_b200_comm_slice_bytes`` (ceil(total / nranks) rounded up to 256)."""
+    nranks = max(int(nranks), 1)
+    s = (int(total_bytes) + nranks - 1) // nranks
+    return (s + 255) & ~255
+
+
+def replica_slice(total_bytes, nranks, rank):
+    """Byte range [lo, hi) of a replicated array that rank ``rank`` uploads itself."""
+    s = slice_bytes(total_bytes, nranks)
+    lo = min(s * rank, total_bytes)
+    return lo, min(lo + s, total_bytes)
+
+
+def init_library_comm(group=None):
+    """Creates libcomet_b200's own communicator for the ranks of a torch.distributed group: rank 0 asks the
+    library for a unique id, the id travels through torch.distributed, every rank calls
+    comet_b200_comm_init with its CUDA device current.  Returns (nranks, rank)."""
+    from . import _lib
+    lib = _lib.load()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if lib.comet_b200_comm_nranks() == world:
+        return world, rank
+    ident = [None]
+    if rank == 0 and world > 1:
+        buf = ctypes.create_string_buffer(128)
+        _lib.check(lib.comet_b200_comm_unique_id(buf, 128))
+        ident = [buf.raw]
+    if world > 1:
+        dist.broadcast_object_list(ident, src=0, group=group)
+        torch.cuda.synchronize()
+    _lib.check(lib.comet_b200_comm_init(world, rank, ident[0]))
+    return world, rank
+
+
+def destroy_library_comm():
+    from . import _lib
+    _lib.check(_lib.load().comet_b200_comm_destroy())
 
 
 def row_blocks(pos, nparts, weights=None):

@@ -302,6 +302,75 @@ COMET_B200_EXPORT void comet_b200_masked_spgemm_count_f64_i32(
     int32_t semiring, int64_t out_rank, void *out_ptr);
 
 /* ------------------------------------------------------------------------- */
+/* Several GPUs: one process per GPU, one row block of the left operand per    */
+/* rank.  COMET itself has no collective and no multi-device runtime (its      */
+/* generated code calls the runtime from one host thread,                      */
+/* lib/Dialect/TensorAlgebra/Transforms/TensorDeclLowering.cpp:937-1052), so   */
+/* these entry points have no counterpart there; they are how a COMET program  */
+/* started once per GPU (mpirun, torchrun) spreads one operation over a node.  */
+/*                                                                             */
+/* Set-up: rank 0 calls comet_b200_comm_unique_id, the host program hands the  */
+/* 128 bytes to every rank (MPI_Bcast, a file, a socket), and every rank calls */
+/* comet_b200_comm_init with its CUDA device current.  NCCL is loaded with     */
+/* dlopen at that moment; single-GPU programs never touch it.                  */
+/*                                                                             */
+/* The *_sharded_* entry points take the same argument lists as the plain ones */
+/* with this meaning: the LEFT sparse operand (A, S), the mask M, the dense X  */
+/* of SDDMM and every OUTPUT are this rank's contiguous row block (row pointer */
+/* starting at 0); the RIGHT operand (B, D = Y, B of the sparse product) is    */
+/* the whole matrix and must hold the same contents on every rank.  Each rank  */
+/* uploads one N-th of the right operand over its own PCIe link, the slices    */
+/* are exchanged between the GPUs (ncclAllGather into each GPU's own memory),  */
+/* and the single-GPU kernels run on local memory.  The calls are collective:  */
+/* every rank makes the same call in the same order; a rank whose operands     */
+/* are refused makes all ranks return with an error instead of leaving the     */
+/* others waiting.                                                             */
+/* ------------------------------------------------------------------------- */
+COMET_B200_EXPORT int32_t comet_b200_comm_unique_id(void *id_out, int64_t id_bytes);   /* id_bytes >= 128 */
+COMET_B200_EXPORT int32_t comet_b200_comm_init(int32_t nranks, int32_t rank, const void *id);
+COMET_B200_EXPORT int32_t comet_b200_comm_nranks(void);   /* 0 without a communicator */
+COMET_B200_EXPORT int32_t comet_b200_comm_rank(void);     /* -1 without a communicator */
+COMET_B200_EXPORT int32_t comet_b200_comm_destroy(void);
+/* bytes of one slice when `total_bytes` of a replicated array are exchanged between `nranks` ranks:
+   ceil(total / nranks) rounded up to 256 (a pure function; needs no device) */
+COMET_B200_EXPORT int64_t comet_b200_comm_slice_bytes(int64_t total_bytes, int32_t nranks);
+
+COMET_B200_EXPORT void comet_b200_spmm_sharded_f64_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                                                       int64_t C_rank, void *C_ptr, int32_t semiring,
+                                                       int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_sddmm_sharded_f64_i64(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr,
+                                                        int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O));
+/* sizes: as in the plain call for this rank's block; when the memref holds 13 entries or more,
+   sizes[11] = entries held by the blocks of the lower ranks (this block's offset in the whole C2crd / Cval)
+   and sizes[12] = entries of all blocks together (one ncclAllGather of the per-rank counts).  Finish
+   with comet_b200_spgemm_numeric_f64_i64 on the block's own arrays. */
+COMET_B200_EXPORT int64_t comet_b200_spgemm_symbolic_sharded_f64_i64(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr);
+/* out[0] = the count over the blocks of ALL ranks (ncclAllReduce on the stream of the counting kernels) */
+COMET_B200_EXPORT void comet_b200_masked_spgemm_count_sharded_f64_i64(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t out_rank, void *out_ptr);
+COMET_B200_EXPORT void comet_b200_spmm_sharded_f64_i32(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                                                       int64_t C_rank, void *C_ptr, int32_t semiring,
+                                                       int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_sddmm_sharded_f64_i32(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr,
+                                                        int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O));
+COMET_B200_EXPORT int64_t comet_b200_spgemm_symbolic_sharded_f64_i32(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr);
+COMET_B200_EXPORT void comet_b200_masked_spgemm_count_sharded_f64_i32(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t out_rank, void *out_ptr);
+
+/* Collectives of the device layer on the communicator of the current device, asynchronous on `stream`:
+   sum of n int64 in place; all[r] = rank r's *one; completion of a buffer of nranks slices of slice_bytes
+   of which this rank has filled slice number rank. */
+COMET_B200_EXPORT int32_t comet_b200_dev_allreduce_sum_i64(int64_t *buf, int64_t n, void *stream);
+COMET_B200_EXPORT int32_t comet_b200_dev_allgather_i64(const int64_t *one, int64_t *all, void *stream);
+COMET_B200_EXPORT int32_t comet_b200_dev_allgather_slices(void *buf, int64_t slice_bytes, void *stream);
+
+/* ------------------------------------------------------------------------- */
 /* Error reporting (COMET's runtime has none beyond stderr + exit; see         */
 /* SparseUtils.cpp:158-168).                                                   */
 /* ------------------------------------------------------------------------- */
@@ -314,6 +383,18 @@ COMET_B200_EXPORT int32_t comet_b200_version(void);
 /* `stream` is a cudaStream_t (NULL = default stream).  row_ids, when not      */
 /* NULL, maps stored row r to its coordinate (the A1crd array of DCSR) and     */
 /* nrows is then the number of stored rows.  Returns 0 on success.             */
+/*                                                                             */
+/* Preconditions the device layer does not check (layer 1 checks them before   */
+/* it calls down): nnz equals pos[nrows] -- work lists are sized from it, and  */
+/* with a smaller value long rows would be left out --, pos starts at 0 and    */
+/* never decreases, every coordinate lies inside the matrix.                   */
+/*                                                                             */
+/* Concurrency: the entry points of this layer keep their work lists, counters */
+/* and narrowed index copies in ONE scratch area per device, which is reused   */
+/* (and grown, with a device synchronisation) from call to call.  Calls on the */
+/* same device must therefore not overlap: issue them from one host thread at  */
+/* a time and onto one stream at a time (or order the streams with events).    */
+/* Different devices are independent.                                          */
 /* ------------------------------------------------------------------------- */
 COMET_B200_EXPORT int32_t comet_b200_dev_spmv_f64_i64(int64_t nrows, int64_t nnz,
                                                       const int64_t *row_ids,
@@ -434,7 +515,9 @@ COMET_B200_EXPORT int32_t comet_b200_dev_spgemm_numeric_f64_i64(int64_t handle, 
 /* *count_dev (device memory, int64) receives the number of products A[i,k]*B[k,j]
    with (i,j) stored in M, over rows [row_lo, row_hi) of A and M.  A duplicate
    coordinate in M counts once (a mask bit), one in A or B counts per occurrence,
-   as in the reference's loops; no ordering of coordinates is required. */
+   as in the reference's loops.  Rows of A and B need no ordering; a row of M must
+   hold its coordinates in ascending order (equal ones adjacent), which is how
+   COMET's reader leaves them (lib/ExecutionEngine/SparseUtils.cpp:360-367). */
 COMET_B200_EXPORT int32_t comet_b200_dev_masked_spgemm_count_f64_i64(
     int64_t row_lo, int64_t row_hi, int64_t ncols, int64_t nnz_a, int64_t nnz_b, int64_t nnz_m,
     const int64_t *apos, const int64_t *acrd, const int64_t *bpos, const int64_t *bcrd,

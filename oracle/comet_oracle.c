@@ -602,3 +602,81 @@ ORACLE_API int64_t oracle_masked_pair_count(int64_t row_lo, int64_t row_hi, int6
     free(mask);
     return count;
 }
+
+/* ------------------------------------------------------------------------- */
+/* Row-parallel variants of the two sparse-output paths.  NOT COMET's          */
+/* schedule: COMET emits sequential loops whenever the output is sparse        */
+/* (lib/Conversion/TensorAlgebraToIndexTree/TensorAlgebraToIndexTree.cpp       */
+/* :279-282), so its own CPU time is the single-thread functions above.  These */
+/* exist only so that the benchmark can also print what the host's cores can   */
+/* do with the same algorithm once rows are handed to threads, each with its   */
+/* own workspace (two passes: counts, then prefix sum, then fill).  Results    */
+/* are identical to the sequential functions.                                  */
+/* ------------------------------------------------------------------------- */
+ORACLE_API int64_t oracle_spgemm_rowparallel(int64_t nrows, int64_t ncols, const int64_t *apos,
+                                             const int64_t *acrd, const double *aval,
+                                             const int64_t *bpos, const int64_t *bcrd, const double *bval,
+                                             int semiring, int64_t *cpos, int64_t *ccrd, double *cval)
+{
+    /* pass 1 (ccrd == NULL): per-row counts into cpos[i+1]; pass 2: fill, cpos already scanned */
+    size_t nc = (size_t)(ncols ? ncols : 1);
+#pragma omp parallel
+    {
+        int64_t *mark = (int64_t *)calloc(nc, sizeof(int64_t));
+        double *ws = ccrd ? (double *)calloc(nc, sizeof(double)) : NULL;
+        int64_t *list = ccrd ? (int64_t *)malloc(nc * sizeof(int64_t)) : NULL;
+#pragma omp for schedule(dynamic, 16)
+        for (int64_t i = 0; i < nrows; i++) {
+            int64_t num = 0;
+            for (int64_t p = apos[i]; p < apos[i + 1]; p++) {
+                int64_t k = acrd[p];
+                double av = aval[p];
+                for (int64_t q = bpos[k]; q < bpos[k + 1]; q++) {
+                    int64_t j = bcrd[q];
+                    if (!ccrd) {
+                        if (mark[j] != i + 1) { mark[j] = i + 1; num++; }
+                    } else {
+                        double v = combine(semiring, av, bval[q]);
+                        if (mark[j] == i + 1) ws[j] = reduce(semiring, ws[j], v);
+                        else { mark[j] = i + 1; list[num++] = j; ws[j] = v; }
+                    }
+                }
+            }
+            if (!ccrd) cpos[i + 1] = num;
+            else {
+                qsort(list, (size_t)num, sizeof(int64_t), cmp_i64);
+                int64_t ins = cpos[i];
+                for (int64_t t = 0; t < num; t++) { ccrd[ins] = list[t]; cval[ins] = ws[list[t]]; ins++; }
+            }
+        }
+        free(mark); free(ws); free(list);
+    }
+    if (!ccrd) {
+        cpos[0] = 0;
+        for (int64_t i = 0; i < nrows; i++) cpos[i + 1] += cpos[i];
+    }
+    return cpos[nrows];
+}
+
+ORACLE_API int64_t oracle_masked_pair_count_rowparallel(int64_t row_lo, int64_t row_hi, int64_t ncols,
+                                                        const int64_t *apos, const int64_t *acrd,
+                                                        const int64_t *bpos, const int64_t *bcrd,
+                                                        const int64_t *mpos, const int64_t *mcrd)
+{
+    int64_t count = 0;
+#pragma omp parallel reduction(+ : count)
+    {
+        unsigned char *mask = (unsigned char *)calloc((size_t)(ncols ? ncols : 1), 1);
+#pragma omp for schedule(dynamic, 64)
+        for (int64_t i = row_lo; i < row_hi; i++) {
+            for (int64_t t = mpos[i]; t < mpos[i + 1]; t++) mask[mcrd[t]] = 1;
+            for (int64_t p = apos[i]; p < apos[i + 1]; p++) {
+                int64_t k = acrd[p];
+                for (int64_t q = bpos[k]; q < bpos[k + 1]; q++) count += mask[bcrd[q]];
+            }
+            for (int64_t t = mpos[i]; t < mpos[i + 1]; t++) mask[mcrd[t]] = 0;
+        }
+        free(mask);
+    }
+    return count;
+}

@@ -47,6 +47,8 @@ def lib():
         _lib.oracle_spgemm_symbolic.restype = ctypes.c_int64
         _lib.oracle_elews_csr_csr.restype = ctypes.c_int64
         _lib.oracle_masked_pair_count.restype = ctypes.c_int64
+        _lib.oracle_masked_pair_count_rowparallel.restype = ctypes.c_int64
+        _lib.oracle_spgemm_rowparallel.restype = ctypes.c_int64
         _lib.oracle_reduce_sum.restype = ctypes.c_double
     return _lib
 
@@ -275,6 +277,30 @@ def spgemm(A, B, M=None, semiring=PLUS_TIMES):
                             _p(ccrd), _p(cval))
     return SparseArrays("CSR", A.nrows, B.ncols, np.array([A.nrows], dtype=np.int64),
                         np.array([-1], dtype=np.int64), cpos, ccrd[:nnz], cval[:nnz])
+
+
+def spgemm_rowparallel(A, B, semiring=PLUS_TIMES):
+    """C = A*B with the rows of A handed to OpenMP threads, a workspace per thread.  NOT COMET's schedule
+    (its sparse-output loops are sequential); same result as ``spgemm``.  For the benchmark's second CPU figure."""
+    L = lib()
+    apos, acrd, aval = _i64(A.a2pos), _i64(A.a2crd), _f64(A.val)
+    bpos, bcrd, bval = _i64(B.a2pos), _i64(B.a2crd), _f64(B.val)
+    cpos = np.zeros(A.nrows + 1, dtype=np.int64)
+    args = (_l(A.nrows), _l(B.ncols), _p(apos), _p(acrd), _p(aval), _p(bpos), _p(bcrd), _p(bval), int(semiring))
+    nnz = L.oracle_spgemm_rowparallel(*args, _p(cpos), None, None)
+    ccrd = np.zeros(max(nnz, 1), dtype=np.int64)
+    cval = np.zeros(max(nnz, 1))
+    L.oracle_spgemm_rowparallel(*args, _p(cpos), _p(ccrd), _p(cval))
+    return SparseArrays("CSR", A.nrows, B.ncols, np.array([A.nrows], dtype=np.int64),
+                        np.array([-1], dtype=np.int64), cpos, ccrd[:nnz], cval[:nnz])
+
+
+def masked_pair_count_rowparallel(A, B, M, row_lo=0, row_hi=None):
+    """``masked_pair_count`` with the rows handed to OpenMP threads (NOT COMET's schedule); same count."""
+    row_hi = A.nrows if row_hi is None else row_hi
+    return int(lib().oracle_masked_pair_count_rowparallel(
+        _l(row_lo), _l(row_hi), _l(B.ncols), _p(_i64(A.a2pos)), _p(_i64(A.a2crd)),
+        _p(_i64(B.a2pos)), _p(_i64(B.a2crd)), _p(_i64(M.a2pos)), _p(_i64(M.a2crd))))
 
 
 def reduce_sum(vals):

@@ -110,3 +110,69 @@ def test_sharded_collectives_world2_gloo():
         assert p.exitcode == 0
     for rank, *oks in results:
         assert all(oks), (rank, oks)
+
+
+# ---------------------------------------------------------------------------
+# The call sequence of the sharded host entry points, replayed on CPU ranks (gloo): every rank uploads
+# only its slice of the replicated operand, the slices are all-gathered, each rank works on its row
+# block, per-rank entry counts are all-gathered and the count is all-reduced.  The slice arithmetic is
+# the library's own (comet_b200_comm_slice_bytes is a pure function and needs no device).
+# ---------------------------------------------------------------------------
+def test_slice_rule_matches_the_library_and_covers_the_array():
+    from comet_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(0)
+    for total in [0, 1, 255, 256, 257, 4096, 10 ** 6 + 3, 1073741824, 8589934591] + list(rng.integers(1, 1 << 34, 50)):
+        for n in range(1, 9):
+            s = sharding.slice_bytes(total, n)
+            assert s == lib.comet_b200_comm_slice_bytes(int(total), n)
+            assert s % 256 == 0 and s * n >= total
+            ranges = [sharding.replica_slice(int(total), n, r) for r in range(n)]
+            assert ranges[0][0] == 0 and ranges[-1][1] == total
+            assert all(ranges[r][1] == ranges[r + 1][0] or ranges[r + 1][0] == total for r in range(n - 1))
+
+
+def _replica_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        A = datasets.rmat_csr(9, 8, seed=4)
+        B = datasets.dense_uniform((A.ncols, 10), 6)             # 40 KB: slices end inside a row
+        raw = np.frombuffer(B.tobytes(), dtype=np.uint8)
+        s = sharding.slice_bytes(raw.nbytes, world)
+        lo, hi = sharding.replica_slice(raw.nbytes, world, rank)
+        mine = torch.zeros(s, dtype=torch.uint8)                  # what this rank sends through its own link
+        mine[:hi - lo] = torch.from_numpy(raw[lo:hi].copy())
+        parts = [torch.empty(s, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(parts, mine)                              # ncclAllGather in the library
+        Bfull = np.frombuffer(torch.cat(parts).numpy()[:raw.nbytes].tobytes(), dtype=np.float64).reshape(B.shape)
+        ok_rep = np.array_equal(Bfull, B)
+        b = sharding.row_blocks(A.a2pos, world)
+        blk = sharding.take_rows(A, int(b[rank]), int(b[rank + 1]))
+        ob = oracle.SparseArrays("CSR", blk.nrows, blk.ncols, blk.a1pos, blk.a1crd, blk.a2pos, blk.a2crd, blk.val)
+        full = oracle.SparseArrays("CSR", A.nrows, A.ncols, A.a1pos, A.a1crd, A.a2pos, A.a2crd, A.val)
+        Cb = torch.from_numpy(oracle.spmm(ob, Bfull))
+        C = sharding.all_gather_rows(Cb, b).numpy()
+        ok_spmm = np.array_equal(C, oracle.spmm(full, B))
+        # the agreement step: one rank reports a fault, every rank sees it
+        flag = torch.tensor([1 if rank == world - 1 else 0])
+        dist.all_reduce(flag)
+        q.put((rank, ok_rep, ok_spmm, int(flag.item()) == 1))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_replicated_operand_by_slices_world2_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_replica_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, *oks in results:
+        assert all(oks), (rank, oks)

@@ -74,3 +74,20 @@ def test_transpose_restatement_against_scipy():
     Tc = oracle.transpose(C)
     assert Tc.a1crd.tolist() == [0, 2, 3, 3] and Tc.a2crd.tolist() == [2, 0, 1, 1]
     assert Tc.val.tolist() == [4.0, 1.0, 2.0, 3.0]
+
+
+def test_rowparallel_variants_equal_the_sequential_oracle():
+    """The row-parallel CPU variants (a second, clearly labelled baseline: not COMET's schedule) give the
+    same arrays and the same count as the sequential restatement."""
+    import numpy as np
+    from comet_b200 import datasets
+    from oracle import oracle
+    A = datasets.rmat_csr(10, 8, seed=2)
+    oa = oracle.SparseArrays("CSR", A.nrows, A.ncols, A.a1pos, A.a1crd, A.a2pos, A.a2crd, A.val)
+    ref, par = oracle.spgemm(oa, oa), oracle.spgemm_rowparallel(oa, oa)
+    assert np.array_equal(ref.a2pos, par.a2pos) and np.array_equal(ref.a2crd, par.a2crd)
+    assert np.array_equal(ref.val, par.val)
+    L = datasets.config_triangles(scale=10, edge_factor=8)
+    ol = oracle.SparseArrays("CSR", L.nrows, L.ncols, L.a1pos, L.a1crd, L.a2pos, L.a2crd, L.val)
+    assert oracle.masked_pair_count(ol, ol, ol) == oracle.masked_pair_count_rowparallel(ol, ol, ol)
+    assert oracle.masked_pair_count(ol, ol, ol, 100, 700) == oracle.masked_pair_count_rowparallel(ol, ol, ol, 100, 700)
