@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "comm.cuh"
+#include "hostcopy.cuh"
 
 extern "C" {
 // device-pointer layer (declared in include/comet_b200.h)
@@ -159,7 +160,7 @@ struct DevBag {
     int upload(void **p, const void *host, size_t bytes)
     {
         CB_TRY(alloc(p, bytes));
-        if (bytes) CB_CUDA(cudaMemcpyAsync(*p, host, bytes, cudaMemcpyHostToDevice, st));
+        if (bytes) CB_TRY(h2d(*p, host, bytes, st));
         return 0;
     }
     // An array every rank needs whole (the replicated operand of a sharded call): without a
@@ -174,7 +175,7 @@ struct DevBag {
         const size_t lo = s * (size_t)cm->rank;
         if (lo < bytes) {
             const size_t n = bytes - lo < s ? bytes - lo : s;
-            CB_CUDA(cudaMemcpyAsync((char *)*p + lo, (const char *)host + lo, n, cudaMemcpyHostToDevice, st));
+            CB_TRY(h2d((char *)*p + lo, (const char *)host + lo, n, st));
         }
         return comm_allgather_inplace(cm, *p, s, st);
     }
@@ -269,10 +270,11 @@ static int verify_coords(const char *what, DevBag &bag, const int64_t *cols, int
     return 0;
 }
 
+// End of a host entry point: the stream's work is done and every staged copy has reached the caller's arrays.
 static int finish(cudaStream_t st)
 {
     CB_CUDA(cudaStreamSynchronize(st));
-    return 0;
+    return copies_drain();
 }
 
 static int need_stream(cudaStream_t *st)
@@ -353,7 +355,7 @@ static int spmv_host(const HostSparse &A, Arr x, Arr y, int semiring, int accumu
     if (!accumulate && A.fmt == F_DCSR) CB_CUDA(cudaMemsetAsync(dy, 0, (size_t)A.nrows * 8, st));
     CB_TRY(comet_b200_dev_spmv_f64_i64(dA.nrows_k, A.nnz, dA.row_ids, dA.pos, dA.crd, dA.val, dx, dy,
                                        semiring, accumulate, st));
-    CB_CUDA(cudaMemcpyAsync(y.data, dy, (size_t)A.nrows * 8, cudaMemcpyDeviceToHost, st));
+    CB_TRY(d2h(y.data, dy, (size_t)A.nrows * 8, st));
     return finish(st);
 }
 
@@ -363,6 +365,36 @@ static int spmv_host(const HostSparse &A, Arr x, Arr y, int semiring, int accumu
 // between the row-major host matrices and packed panels on the device, two buffers each).
 // With a communicator, a rank uploads only its N-th of the rows of each panel of B and the panel is
 // completed by an all-gather on the compute stream before the kernel that reads it.
+// The events and the drain of the panel pipeline: whatever way the pipeline function leaves, the copy
+// streams are drained and the events destroyed before the panel buffers go back to the pool.
+struct PanelSync {
+    cudaStream_t up, down, st;
+    cudaEvent_t ev[7];
+    int n = 0;
+    PanelSync(cudaStream_t u, cudaStream_t d, cudaStream_t s) : up(u), down(d), st(s) {}
+    int create(cudaEvent_t **out)
+    {
+        CB_CUDA(cudaEventCreateWithFlags(&ev[n], cudaEventDisableTiming));
+        *out = &ev[n++];
+        return 0;
+    }
+    int drain()
+    {
+        cudaError_t e1 = cudaStreamSynchronize(up), e2 = cudaStreamSynchronize(down), e3 = cudaStreamSynchronize(st);
+        int rc = copies_drain();
+        if (!rc && (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess)) rc = fail("spmm: panel pipeline failed");
+        return rc;
+    }
+    ~PanelSync()
+    {
+        cudaStreamSynchronize(up);
+        cudaStreamSynchronize(down);
+        cudaStreamSynchronize(st);
+        copies_drain();
+        for (int i = 0; i < n; i++) cudaEventDestroy(ev[i]);
+    }
+};
+
 static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &bag, const Mat &B, const Mat &C,
                             int semiring, int64_t panel, cudaStream_t st, Comm *cm)
 {
@@ -374,50 +406,41 @@ static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &ba
     const int64_t my_lo = slice_rows * rank < A.ncols ? slice_rows * rank : A.ncols;
     const int64_t my_rows = A.ncols - my_lo < slice_rows ? A.ncols - my_lo : slice_rows;
     double *dB[2], *dC[2];
-    cudaEvent_t in[2], comp[2], out[2];
     for (int i = 0; i < 2; i++) {
         CB_TRY(bag.alloc((void **)&dB[i], (size_t)slice_rows * nranks * panel * 8));
         CB_TRY(bag.alloc((void **)&dC[i], (size_t)A.nrows * panel * 8));
-        CB_CUDA(cudaEventCreateWithFlags(&in[i], cudaEventDisableTiming));
-        CB_CUDA(cudaEventCreateWithFlags(&comp[i], cudaEventDisableTiming));
-        CB_CUDA(cudaEventCreateWithFlags(&out[i], cudaEventDisableTiming));
     }
-    cudaEvent_t ready;
-    CB_CUDA(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
-    CB_CUDA(cudaEventRecord(ready, st));                 // A is uploaded, panel buffers exist
-    CB_CUDA(cudaStreamWaitEvent(up, ready, 0));
-    CB_CUDA(cudaStreamWaitEvent(down, ready, 0));
-    int rc = 0;
+    PanelSync sync(up, down, st);        // declared after the buffers: it drains before they are freed
+    cudaEvent_t *in[2], *comp[2], *out[2], *ready;
+    for (int i = 0; i < 2; i++) {
+        CB_TRY(sync.create(&in[i]));
+        CB_TRY(sync.create(&comp[i]));
+        CB_TRY(sync.create(&out[i]));
+    }
+    CB_TRY(sync.create(&ready));
+    CB_CUDA(cudaEventRecord(*ready, st));                 // A is uploaded, panel buffers exist
+    CB_CUDA(cudaStreamWaitEvent(up, *ready, 0));
+    CB_CUDA(cudaStreamWaitEvent(down, *ready, 0));
     int64_t j = 0;
-    for (int64_t c0 = 0; c0 < k && !rc; c0 += panel, j++) {
+    for (int64_t c0 = 0; c0 < k; c0 += panel, j++) {
         const int b = (int)(j & 1);
         const int64_t w = (k - c0) < panel ? (k - c0) : panel;
-        if (j >= 2) CB_CUDA(cudaStreamWaitEvent(up, comp[b], 0));       // panel j-2 no longer reads dB[b]
+        if (j >= 2) CB_CUDA(cudaStreamWaitEvent(up, *comp[b], 0));       // panel j-2 no longer reads dB[b]
         if (my_rows > 0)
-            CB_CUDA(cudaMemcpy2DAsync(dB[b] + my_lo * panel, (size_t)panel * 8, B.data + my_lo * B.s0 + c0,
-                                      (size_t)B.s0 * 8, (size_t)w * 8, (size_t)my_rows, cudaMemcpyHostToDevice, up));
-        CB_CUDA(cudaEventRecord(in[b], up));
-        CB_CUDA(cudaStreamWaitEvent(st, in[b], 0));
-        if (nranks > 1) {
-            rc = comm_allgather_inplace(cm, dB[b], (size_t)slice_rows * panel * 8, st);
-            if (rc) break;
-        }
-        if (j >= 2) CB_CUDA(cudaStreamWaitEvent(st, out[b], 0));        // panel j-2 has left dC[b]
-        rc = comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, w, dA.row_ids, dA.pos, dA.crd, dA.val, dB[b],
-                                         panel, dC[b], panel, semiring, 0, 0, st);
-        if (rc) break;
-        CB_CUDA(cudaEventRecord(comp[b], st));
-        CB_CUDA(cudaStreamWaitEvent(down, comp[b], 0));
-        CB_CUDA(cudaMemcpy2DAsync(C.data + c0, (size_t)C.s0 * 8, dC[b], (size_t)panel * 8, (size_t)w * 8,
-                                  (size_t)A.nrows, cudaMemcpyDeviceToHost, down));
-        CB_CUDA(cudaEventRecord(out[b], down));
+            CB_TRY(h2d_2d(dB[b] + my_lo * panel, (size_t)panel * 8, B.data + my_lo * B.s0 + c0, (size_t)B.s0 * 8,
+                          (size_t)w * 8, (size_t)my_rows, up));
+        CB_CUDA(cudaEventRecord(*in[b], up));
+        CB_CUDA(cudaStreamWaitEvent(st, *in[b], 0));
+        if (nranks > 1) CB_TRY(comm_allgather_inplace(cm, dB[b], (size_t)slice_rows * panel * 8, st));
+        if (j >= 2) CB_CUDA(cudaStreamWaitEvent(st, *out[b], 0));        // panel j-2 has left dC[b]
+        CB_TRY(comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, w, dA.row_ids, dA.pos, dA.crd, dA.val, dB[b],
+                                           panel, dC[b], panel, semiring, 0, 0, st));
+        CB_CUDA(cudaEventRecord(*comp[b], st));
+        CB_CUDA(cudaStreamWaitEvent(down, *comp[b], 0));
+        CB_TRY(d2h_2d(C.data + c0, (size_t)C.s0 * 8, dC[b], (size_t)panel * 8, (size_t)w * 8, (size_t)A.nrows, down));
+        CB_CUDA(cudaEventRecord(*out[b], down));
     }
-    cudaError_t e1 = cudaStreamSynchronize(up), e2 = cudaStreamSynchronize(down), e3 = cudaStreamSynchronize(st);
-    for (int i = 0; i < 2; i++) { cudaEventDestroy(in[i]); cudaEventDestroy(comp[i]); cudaEventDestroy(out[i]); }
-    cudaEventDestroy(ready);
-    if (rc) return rc;
-    if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) return fail("spmm: panel pipeline failed");
-    return 0;
+    return sync.drain();
 }
 
 static int spmm_check(const HostSparse &A, const Mat &B, const Mat &C)
@@ -465,7 +488,7 @@ static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiri
     if (!accumulate && A.fmt == F_DCSR) CB_CUDA(cudaMemsetAsync(dC, 0, cbytes, st));
     CB_TRY(comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, k, dA.row_ids, dA.pos, dA.crd,
                                        dA.val, dB, B.s0, dC, C.s0, semiring, accumulate, 0, st));
-    if (cbytes) CB_CUDA(cudaMemcpyAsync(C.data, dC, cbytes, cudaMemcpyDeviceToHost, st));
+    if (cbytes) CB_TRY(d2h(C.data, dC, cbytes, st));
     return finish(st);
 }
 
@@ -596,10 +619,7 @@ static void sddmm_impl(int mode, COMET_B200_SPARSE2D(S), int64_t X_rank, void *X
     if (bag.alloc((void **)&dOut, (size_t)S.nnz * 8)) return;
     if (comet_b200_dev_sddmm_f64_i64(S.nrows, S.nnz, k, dS.pos, dS.crd, dS.val, dX, X.s0, dY, ldy, dOut, st))
         return;
-    if (S.nnz && cudaMemcpyAsync(O.val, dOut, (size_t)S.nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
-        fail("sddmm: copy of the result failed");
-        return;
-    }
+    if (S.nnz && d2h(O.val, dOut, (size_t)S.nnz * 8, st)) return;
     copy_pattern(S, O);
     finish(st);
 }
@@ -632,10 +652,7 @@ static void elews_sd_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank, void 
     if (comet_b200_dev_elews_mul_sparse_dense_f64_i64(A.nrows, A.nnz, dA.pos, dA.rows, dA.crd, dA.val, dB,
                                                       B.s0, dOut, st))
         return;
-    if (A.nnz && cudaMemcpyAsync(C.val, dOut, (size_t)A.nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
-        fail("elews_mul: copy of the result failed");
-        return;
-    }
+    if (A.nnz && d2h(C.val, dOut, (size_t)A.nnz * 8, st)) return;
     copy_pattern(A, C);
     finish(st);
 }
@@ -679,10 +696,7 @@ static void elews_to_dense_impl(int isz, COMET_B200_SPARSE2D(A), int64_t B_rank,
     if (comet_b200_dev_elews_mul_sparse_dense_to_dense_f64_i64(nstored, A.nnz, dA.row_ids, dA.pos, dA.rows, dA.crd,
                                                                dA.val, dB, B.s0, dC, C.s0, st))
         return;
-    if (cbytes && cudaMemcpyAsync(C.data, dC, cbytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
-        fail("elews_mul: copy of the result failed");
-        return;
-    }
+    if (cbytes && d2h(C.data, dC, cbytes, st)) return;
     finish(st);
 }
 
@@ -691,13 +705,13 @@ static int download_idx(DevBag &bag, const int64_t *dev, char *host, int64_t n, 
 {
     if (n <= 0) return 0;
     if (isz == 8) {
-        CB_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * 8, cudaMemcpyDeviceToHost, st));
+        CB_TRY(d2h(host, dev, (size_t)n * 8, st));
         return 0;
     }
     int32_t *d32 = nullptr;
     CB_TRY(bag.alloc((void **)&d32, (size_t)n * 4));
     CB_TRY(narrow_any_i64_to_i32(dev, d32, n, st));
-    CB_CUDA(cudaMemcpyAsync(host, d32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    CB_TRY(d2h(host, d32, (size_t)n * 4, st));
     return 0;
 }
 
@@ -774,10 +788,7 @@ static void transpose_impl(int isz, int32_t A1format, int32_t A2format, int64_t 
         idx_set((char *)b1pos.data, 1, isz, nnz);
     }
     if (download_idx(bag, ocrd, (char *)b2crd.data, nnz, isz, st)) return;
-    if (nnz && cudaMemcpyAsync(bval.data, oval, (size_t)nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
-        fail("transpose: copy of the values failed");
-        return;
-    }
+    if (nnz && d2h(bval.data, oval, (size_t)nnz * 8, st)) return;
     if (finish(st)) return;
     idx_set((char *)sizes.data, 0, isz, ncols);
     idx_set((char *)sizes.data, 1, isz, nrows);
@@ -822,10 +833,7 @@ static void dense_sparse_impl(int isz, int64_t A_rank, void *A_ptr, COMET_B200_S
     if (comet_b200_dev_dense_times_sparse_f64_i64(m, B.ncols, dB.nrows_k, B.nnz, dB.row_ids, dB.pos, dB.crd, dB.val, dA,
                                                   lda, dC, ldc, semiring, accumulate, st))
         return;
-    if (cbytes && cudaMemcpyAsync(hc, dC, cbytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
-        fail("dense x sparse: copy of the result failed");
-        return;
-    }
+    if (cbytes && d2h(hc, dC, cbytes, st)) return;
     finish(st);
 }
 
@@ -885,8 +893,7 @@ static int64_t sparse_out_symbolic(int isz, int kind, const HostSparse &A, const
         }
         pos_src = p32;
     }
-    if (cudaMemcpyAsync(cpos.data, pos_src, (size_t)(A.nrows + 1) * isz, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
-        cudaStreamSynchronize(st) != cudaSuccess) {
+    if (d2h(cpos.data, pos_src, (size_t)(A.nrows + 1) * isz, st) || finish(st)) {
         comet_b200_handle_destroy(dev_handle);
         return fail("sparse output: copy of C2pos failed"), 0;
     }
@@ -993,12 +1000,11 @@ static void spgemm_numeric_impl(int isz, int64_t handle, int64_t C2crd_rank, voi
         if (!rc) rc = narrow_any_i64_to_i32(dcrd, dcrd32, hp->nnz, st);
     }
     if (!rc && hp->nnz) {
-        if (cudaMemcpyAsync(crd.data, isz == 4 ? (void *)dcrd32 : (void *)dcrd, (size_t)hp->nnz * isz,
-                            cudaMemcpyDeviceToHost, st) != cudaSuccess ||
-            cudaMemcpyAsync(val.data, dval, (size_t)hp->nnz * 8, cudaMemcpyDeviceToHost, st) != cudaSuccess)
-            rc = fail("numeric phase: copy of the result failed");
+        if (d2h(crd.data, isz == 4 ? (void *)dcrd32 : (void *)dcrd, (size_t)hp->nnz * isz, st) ||
+            d2h(val.data, dval, (size_t)hp->nnz * 8, st))
+            rc = 1;
     }
-    if (cudaStreamSynchronize(st) != cudaSuccess && !rc) fail("numeric phase: synchronize failed");
+    if (finish(st) && !rc) fail("numeric phase: synchronize failed");
     if (dcrd) cudaFreeAsync(dcrd, st);
     if (dcrd32) cudaFreeAsync(dcrd32, st);
     if (dval) cudaFreeAsync(dval, st);

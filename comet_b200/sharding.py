@@ -71,12 +71,14 @@ def row_blocks(pos, nparts, weights=None):
     if weights is None:
         cum = pos - pos[0]
     else:
-        cum = np.concatenate([[0], np.cumsum(np.asarray(weights, dtype=np.int64))])
-    total = int(cum[-1])
+        w = np.asarray(weights)
+        w = w.astype(np.float64) if w.dtype.kind == "f" else w.astype(np.int64)     # measured costs are fractional
+        cum = np.concatenate([np.zeros(1, dtype=w.dtype), np.cumsum(w)])
+    total = cum[-1]
     bounds = np.zeros(nparts + 1, dtype=np.int64)
     bounds[nparts] = nrows
     for p in range(1, nparts):
-        target = (total * p) // nparts
+        target = (total * p) / nparts if cum.dtype.kind == "f" else (int(total) * p) // nparts
         bounds[p] = int(np.searchsorted(cum, target, side="left"))
     bounds = np.minimum(np.maximum.accumulate(bounds), nrows)
     return bounds

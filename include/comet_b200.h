@@ -523,6 +523,16 @@ COMET_B200_EXPORT int32_t comet_b200_dev_masked_spgemm_count_f64_i64(
     const int64_t *apos, const int64_t *acrd, const int64_t *bpos, const int64_t *bcrd,
     const int64_t *mpos, const int64_t *mcrd, int64_t *count_dev, void *stream);
 
+/* Measurement aid (no counterpart in the reference): the bare gather SpMM / SDDMM are built around.  For
+   each of the nnz column indices the k-double row b[crd[p], :] is read and folded into a sum; out
+   (device, at least 8 * ctas_per_sm * SM-count doubles) receives one partial sum per warp.  fold_rows > 0
+   maps every index into the first fold_rows rows (a working set that fits L2).  Timing it over a
+   benchmark's column stream gives the rate a gather-per-entry kernel is bounded by on that stream. */
+COMET_B200_EXPORT int32_t comet_b200_dev_gather_probe_f64_i64(int64_t nnz, const int64_t *crd, const double *b,
+                                                              int64_t ldb, int64_t k, int64_t fold_rows,
+                                                              int32_t ctas_per_sm, double *out, int64_t out_len,
+                                                              void *stream);
+
 /* Frees the library's scratch memory on the current device. */
 COMET_B200_EXPORT void comet_b200_release_scratch(void);
 
