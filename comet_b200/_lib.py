@@ -86,8 +86,21 @@ SIGNATURES = {
                                                       c_void_p, c_int64, c_void_p]),
 }
 
+# cometpy's calling convention (_mlir_ciface_<kernel>): result pointers first, a CSR input as seven arguments
+_CI_CSR = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
+for _w in ("i64", "i32"):
+    SIGNATURES.update({
+        "_mlir_ciface_comet_b200_spmv_csr_f64_" + _w: (None, [c_void_p] + _CI_CSR + [c_void_p]),
+        "_mlir_ciface_comet_b200_spmm_csr_f64_" + _w: (None, [c_void_p] + _CI_CSR + [c_void_p]),
+        "_mlir_ciface_comet_b200_spgemm_csr_f64_" + _w: (None, [c_void_p] + _CI_CSR * 2 + [c_int64]),
+        "_mlir_ciface_comet_b200_spgemm_masked_csr_f64_" + _w: (None, [c_void_p] + _CI_CSR * 3 + [c_int64]),
+        "_mlir_ciface_comet_b200_masked_count_csr_f64_" + _w: (c_double, _CI_CSR * 3),
+        "_mlir_ciface_comet_b200_sddmm_csr_f64_" + _w: (None, [c_void_p] + _CI_CSR + [c_void_p, c_void_p]),
+    })
+SIGNATURES["comet_b200_ciface_free"] = (None, [c_void_p])
+
 # the host entry points exist once per index width
-for _name in [n for n in SIGNATURES if n.endswith("_f64_i64") and "_dev_" not in n]:
+for _name in [n for n in SIGNATURES if n.endswith("_f64_i64") and "_dev_" not in n and not n.startswith("_mlir")]:
     SIGNATURES[_name[:-4] + "_i32"] = SIGNATURES[_name]
 
 _lib = None

@@ -421,6 +421,15 @@ static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &ba
     CB_CUDA(cudaEventRecord(*ready, st));                 // A is uploaded, panel buffers exist
     CB_CUDA(cudaStreamWaitEvent(up, *ready, 0));
     CB_CUDA(cudaStreamWaitEvent(down, *ready, 0));
+    // tracing: a timed event after every upload, kernel and download, reported against `t0` at the end
+    const bool tracing = getenv("COMET_B200_TRACE") != nullptr;
+    std::vector<cudaEvent_t> tev;
+    auto mark = [&](cudaStream_t s) {
+        if (!tracing) return;
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) == cudaSuccess) { cudaEventRecord(e, s); tev.push_back(e); }
+    };
+    mark(st);
     int64_t j = 0;
     for (int64_t c0 = 0; c0 < k; c0 += panel, j++) {
         const int b = (int)(j & 1);
@@ -430,17 +439,31 @@ static int spmm_host_panels(const HostSparse &A, const DevSparse &dA, DevBag &ba
             CB_TRY(h2d_2d(dB[b] + my_lo * panel, (size_t)panel * 8, B.data + my_lo * B.s0 + c0, (size_t)B.s0 * 8,
                           (size_t)w * 8, (size_t)my_rows, up));
         CB_CUDA(cudaEventRecord(*in[b], up));
+        mark(up);
+        trace("spmm: panel %lld upload enqueued", (long long)j);
         CB_CUDA(cudaStreamWaitEvent(st, *in[b], 0));
         if (nranks > 1) CB_TRY(comm_allgather_inplace(cm, dB[b], (size_t)slice_rows * panel * 8, st));
         if (j >= 2) CB_CUDA(cudaStreamWaitEvent(st, *out[b], 0));        // panel j-2 has left dC[b]
         CB_TRY(comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, w, dA.row_ids, dA.pos, dA.crd, dA.val, dB[b],
                                            panel, dC[b], panel, semiring, 0, 0, st));
         CB_CUDA(cudaEventRecord(*comp[b], st));
+        mark(st);
         CB_CUDA(cudaStreamWaitEvent(down, *comp[b], 0));
         CB_TRY(d2h_2d(C.data + c0, (size_t)C.s0 * 8, dC[b], (size_t)panel * 8, (size_t)w * 8, (size_t)A.nrows, down));
         CB_CUDA(cudaEventRecord(*out[b], down));
+        mark(down);
+        trace("spmm: panel %lld download enqueued", (long long)j);
     }
-    return sync.drain();
+    const int drc = sync.drain();
+    trace("spmm: drained");
+    for (size_t i = 1; i < tev.size(); i++) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, tev[0], tev[i]);
+        trace("spmm: device time, panel %zu %s done at %.3f ms", (i - 1) / 3,
+              (i - 1) % 3 == 0 ? "upload" : ((i - 1) % 3 == 1 ? "all-gather + kernel" : "download"), ms);
+    }
+    for (cudaEvent_t e : tev) cudaEventDestroy(e);
+    return drc;
 }
 
 static int spmm_check(const HostSparse &A, const Mat &B, const Mat &C)
@@ -460,9 +483,13 @@ static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiri
     ShardGuard guard(cm, st);
     DevBag bag(st);
     DevSparse dA;
+    trace("spmm: begin (%lld rows, %lld entries, rank %d of %d)", (long long)A.nrows, (long long)A.nnz,
+          cm ? cm->rank : 0, cm ? cm->nranks : 1);
     int rc = spmm_check(A, B, C);
     if (!rc) rc = upload_sparse("spmm", A, bag, &dA);
+    trace("spmm: A uploaded and checked");
     CB_TRY(guard.agree(rc));
+    trace("spmm: ranks agreed");
     const int64_t k = B.cols;
     {
         // panels of 32 columns (256-byte rows) once the dense operands are big enough to matter

@@ -19,6 +19,10 @@ namespace cb200 {
 int fail(const char *fmt, ...);   // always returns a non-zero status
 void clear_error();
 
+// With COMET_B200_TRACE set, phases of the host entry points are logged on stderr with a wall-clock
+// stamp (milliseconds since the first line): where the time of an end-to-end call goes.
+void trace(const char *fmt, ...);
+
 #define CB_CUDA(expr)                                                               \
     do {                                                                            \
         cudaError_t e_ = (expr);                                                    \

@@ -1,6 +1,7 @@
 // Library state: error reporting, per-device scratch slots, the library stream.
 #include <stdarg.h>
 #include <string.h>
+#include <time.h>
 
 #include <mutex>
 
@@ -34,6 +35,25 @@ int fail(const char *fmt, ...)
 }
 
 void clear_error() { g_err[0] = 0; }
+
+void trace(const char *fmt, ...)
+{
+    static int on = -1;
+    static struct timespec t0;
+    if (on < 0) {
+        on = getenv("COMET_B200_TRACE") ? 1 : 0;
+        clock_gettime(CLOCK_MONOTONIC, &t0);
+    }
+    if (!on) return;
+    struct timespec t;
+    clock_gettime(CLOCK_MONOTONIC, &t);
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    fprintf(stderr, "[comet_b200 %10.3f ms] %s\n", (t.tv_sec - t0.tv_sec) * 1e3 + (t.tv_nsec - t0.tv_nsec) * 1e-6, buf);
+}
 
 static const int kMaxDevices = 64;
 struct DeviceState {

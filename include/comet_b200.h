@@ -371,6 +371,56 @@ COMET_B200_EXPORT int32_t comet_b200_dev_allgather_i64(const int64_t *one, int64
 COMET_B200_EXPORT int32_t comet_b200_dev_allgather_slices(void *buf, int64_t slice_bytes, void *stream);
 
 /* ------------------------------------------------------------------------- */
+/* The same operations in the shape cometpy calls its kernels with.            */
+/* cometpy emits each kernel with llvm.emit_c_interface and calls              */
+/* _mlir_ciface_<kernel> through ctypes                                        */
+/* (frontends/numpy-scipy/cometpy/MLIRGen/ops.py:548-553, lowering.py:212-460):*/
+/* results first, one POINTER per shaped result (a memref struct for a dense   */
+/* result; for a CSR result the struct {dims, insert_1, A1pos, insert_2, A2pos,*/
+/* A2crd, Aval} of MLIRGen/utils.py:26-27), filled by the callee with malloc'ed*/
+/* arrays that cometpy wraps without copying (lowering.py:433-448); then the   */
+/* inputs, a dense array as one memref POINTER, a scipy CSR matrix as seven    */
+/* arguments: dims*, insert_pos_1 (by value), A1pos*, insert_pos_2 (by value), */
+/* A2pos*, A2crd*, Aval* (lowering.py:298-321).  A scalar result is returned.  */
+/* `C` / `O` point to the CSR result struct.  The insert positions are         */
+/* ignored.  Release result arrays with comet_b200_ciface_free (= free).       */
+/* ------------------------------------------------------------------------- */
+#define COMET_B200_CIFACE_CSR(P)                                                                      \
+    comet_b200_memref1d *P##dims, int64_t P##insert_1, comet_b200_memref1d *P##1pos, int64_t P##insert_2, \
+        comet_b200_memref1d *P##2pos, comet_b200_memref1d *P##2crd, comet_b200_memref1d *P##val
+
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spmv_csr_f64_i64(comet_b200_memref1d *y, COMET_B200_CIFACE_CSR(A),
+                                                                comet_b200_memref1d *x);
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spmm_csr_f64_i64(comet_b200_memref2d *C, COMET_B200_CIFACE_CSR(A),
+                                                                comet_b200_memref2d *B);
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spgemm_csr_f64_i64(void *C, COMET_B200_CIFACE_CSR(A),
+                                                                  COMET_B200_CIFACE_CSR(B), int64_t semiring);
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spgemm_masked_csr_f64_i64(void *C, COMET_B200_CIFACE_CSR(A),
+                                                                         COMET_B200_CIFACE_CSR(B),
+                                                                         COMET_B200_CIFACE_CSR(M), int64_t semiring);
+COMET_B200_EXPORT double _mlir_ciface_comet_b200_masked_count_csr_f64_i64(COMET_B200_CIFACE_CSR(A),
+                                                                          COMET_B200_CIFACE_CSR(B),
+                                                                          COMET_B200_CIFACE_CSR(M));
+/* Y is the row-major [cols, K] operand */
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_sddmm_csr_f64_i64(void *O, COMET_B200_CIFACE_CSR(S),
+                                                                 comet_b200_memref2d *X, comet_b200_memref2d *Y);
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spmv_csr_f64_i32(comet_b200_memref1d *y, COMET_B200_CIFACE_CSR(A),
+                                                                comet_b200_memref1d *x);
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spmm_csr_f64_i32(comet_b200_memref2d *C, COMET_B200_CIFACE_CSR(A),
+                                                                comet_b200_memref2d *B);
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spgemm_csr_f64_i32(void *C, COMET_B200_CIFACE_CSR(A),
+                                                                  COMET_B200_CIFACE_CSR(B), int64_t semiring);
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_spgemm_masked_csr_f64_i32(void *C, COMET_B200_CIFACE_CSR(A),
+                                                                         COMET_B200_CIFACE_CSR(B),
+                                                                         COMET_B200_CIFACE_CSR(M), int64_t semiring);
+COMET_B200_EXPORT double _mlir_ciface_comet_b200_masked_count_csr_f64_i32(COMET_B200_CIFACE_CSR(A),
+                                                                          COMET_B200_CIFACE_CSR(B),
+                                                                          COMET_B200_CIFACE_CSR(M));
+COMET_B200_EXPORT void _mlir_ciface_comet_b200_sddmm_csr_f64_i32(void *O, COMET_B200_CIFACE_CSR(S),
+                                                                 comet_b200_memref2d *X, comet_b200_memref2d *Y);
+COMET_B200_EXPORT void comet_b200_ciface_free(void *p);
+
+/* ------------------------------------------------------------------------- */
 /* Error reporting (COMET's runtime has none beyond stderr + exit; see         */
 /* SparseUtils.cpp:158-168).                                                   */
 /* ------------------------------------------------------------------------- */

@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _declared():
     text = open(os.path.join(ROOT, "include", "comet_b200.h")).read()
-    return sorted(set(re.findall(r"\b(comet_b200_[A-Za-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b((?:_mlir_ciface_)?comet_b200_[A-Za-z0-9_]+)\s*\(", text)))
 
 
 def test_header_declares_expected_entry_points():
