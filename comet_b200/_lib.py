@@ -103,6 +103,11 @@ SIGNATURES["comet_b200_ciface_free"] = (None, [c_void_p])
 for _name in [n for n in SIGNATURES if n.endswith("_f64_i64") and "_dev_" not in n and not n.startswith("_mlir")]:
     SIGNATURES[_name[:-4] + "_i32"] = SIGNATURES[_name]
 
+# float-valued forms of the main host entry points
+for _op in ("spmv", "spmm", "sddmm", "spgemm_symbolic", "spgemm_numeric"):
+    for _w in ("i64", "i32"):
+        SIGNATURES["comet_b200_%s_f32_%s" % (_op, _w)] = SIGNATURES["comet_b200_%s_f64_i64" % _op]
+
 _lib = None
 
 

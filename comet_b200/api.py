@@ -93,6 +93,13 @@ def _f64(a):
     return np.ascontiguousarray(a, dtype=np.float64)
 
 
+def _vals(a):
+    """Values as the library takes them: float32 arrays stay float32 (they select the _f32_ entry points,
+    as cometpy's element type does), everything else becomes float64."""
+    a = np.asarray(a)
+    return np.ascontiguousarray(a, dtype=np.float32 if a.dtype == np.float32 else np.float64)
+
+
 def as_sparse(m):
     """scipy CSR/COO or a COMET-array object -> SparseTensor (index width kept, values float64)."""
     if isinstance(m, SparseTensor):
@@ -100,16 +107,16 @@ def as_sparse(m):
     if hasattr(m, "a2crd") and hasattr(m, "format") and isinstance(m.format, str) and m.format.isupper():
         dt = _index_dtype(m.a1pos, m.a1crd, m.a2pos, m.a2crd)
         return SparseTensor(m.format, m.nrows, m.ncols, _idx(m.a1pos, dt), _idx(m.a1crd, dt), _idx(m.a2pos, dt),
-                            _idx(m.a2crd, dt), _f64(m.val))
+                            _idx(m.a2crd, dt), _vals(m.val))
     fmt = getattr(m, "format", None)
     if fmt == "csr":
         dt = _index_dtype(m.indptr, m.indices)
         return SparseTensor("CSR", m.shape[0], m.shape[1], np.array([m.shape[0]], dtype=dt),
-                            np.array([-1], dtype=dt), _idx(m.indptr, dt), _idx(m.indices, dt), _f64(m.data))
+                            np.array([-1], dtype=dt), _idx(m.indptr, dt), _idx(m.indices, dt), _vals(m.data))
     if fmt == "coo":
         dt = _index_dtype(m.row, m.col)
         return SparseTensor("COO", m.shape[0], m.shape[1], np.array([0, m.nnz], dtype=dt),
-                            _idx(m.row, dt), np.array([-1], dtype=dt), _idx(m.col, dt), _f64(m.data))
+                            _idx(m.row, dt), np.array([-1], dtype=dt), _idx(m.col, dt), _vals(m.data))
     raise TypeError("unsupported sparse operand: %r (CSR and COO are accepted, like cometpy)" % type(m))
 
 
@@ -153,12 +160,26 @@ class _Packer:
         return args
 
 
-def _entry(lib, name, *tensors):
-    """The entry point of the operands' common index width, and the operands converted to it
-    (mixed widths are promoted to int64, like cometpy does)."""
+_F32_OPS = ("spmv", "spmm", "sddmm", "spgemm_symbolic", "spgemm_numeric")
+
+
+def _entry(lib, name, *tensors, dense=()):
+    """The entry point of the operands' common index width and value type, and the sparse operands
+    converted to that index width (mixed widths are promoted to int64, like cometpy does).  float32 is
+    chosen only when every sparse and dense operand is float32 and the operation has an _f32_ form."""
     dt = np.int32 if all(t.index_dtype == np.int32 for t in tensors) else np.int64
-    fn = getattr(lib, "comet_b200_%s_f64_%s" % (name, "i32" if dt == np.int32 else "i64"))
-    return fn, dt, [t.with_index_dtype(dt) for t in tensors]
+    f32 = (name in _F32_OPS and all(np.asarray(t.val).dtype == np.float32 for t in tensors)
+           and all(np.asarray(d).dtype == np.float32 for d in dense))
+    fn = getattr(lib, "comet_b200_%s_%s_%s" % (name, "f32" if f32 else "f64", "i32" if dt == np.int32 else "i64"))
+    fn.value_dtype = np.float32 if f32 else np.float64
+    out = []
+    for t in tensors:
+        t = t.with_index_dtype(dt)
+        if np.asarray(t.val).dtype != fn.value_dtype:
+            t = SparseTensor(t.format, t.nrows, t.ncols, t.a1pos, t.a1crd, t.a2pos, t.a2crd,
+                             np.ascontiguousarray(t.val, dtype=fn.value_dtype))
+        out.append(t)
+    return fn, dt, out
 
 
 def _semiring(s):
@@ -182,9 +203,10 @@ def spmv(A, x, y0=None, semiring=PLUS_TIMES):
     A = as_sparse(A)
     lib = _lib.load()
     pk = _Packer()
-    x = _f64(x)
-    y = np.zeros(A.nrows) if y0 is None else _f64(y0).copy()
-    fn, _, (A,) = _entry(lib, "spmv", A)
+    fn, _, (A,) = _entry(lib, "spmv", A, dense=(x,) if y0 is None else (x, y0))
+    vt = fn.value_dtype
+    x = np.ascontiguousarray(x, dtype=vt)
+    y = np.zeros(A.nrows, dtype=vt) if y0 is None else np.array(y0, dtype=vt)
     fn(*pk.sparse(A), *pk.m1(x), *pk.m1(y), _dense_semiring(semiring), 0 if y0 is None else 1)
     _lib.check()
     return y
@@ -202,9 +224,10 @@ def spmm(A, B, C0=None, semiring=PLUS_TIMES, sharded=False):
     A = as_sparse(A)
     lib = _lib.load()
     pk = _Packer()
-    B = _f64(B)
-    C = np.zeros((A.nrows, B.shape[1])) if C0 is None else _f64(C0).copy()
-    fn, _, (A,) = _entry(lib, _name("spmm", sharded), A)
+    fn, _, (A,) = _entry(lib, _name("spmm", sharded), A, dense=(B,) if C0 is None else (B, C0))
+    vt = fn.value_dtype
+    B = np.ascontiguousarray(B, dtype=vt)
+    C = np.zeros((A.nrows, B.shape[1]), dtype=vt) if C0 is None else np.array(C0, dtype=vt, order="C")
     fn(*pk.sparse(A), *pk.m2(B), *pk.m2(C), _dense_semiring(semiring), 0 if C0 is None else 1)
     _lib.check()
     return C
@@ -233,11 +256,12 @@ def sddmm(S, X, Y, y_is_kj=False, sharded=False):
     S = as_sparse(S)
     lib = _lib.load()
     pk = _Packer()
-    X, Y = _f64(X), _f64(Y)
+    fn, _, (S,) = _entry(lib, _name("sddmm", sharded), S, dense=(X, Y))
+    vt = fn.value_dtype
+    X, Y = np.ascontiguousarray(X, dtype=vt), np.ascontiguousarray(Y, dtype=vt)
     out = SparseTensor("CSR", S.nrows, S.ncols, np.zeros_like(S.a1pos), np.zeros_like(S.a1crd),
-                       np.zeros_like(S.a2pos), np.zeros_like(S.a2crd), np.zeros(S.nnz))
+                       np.zeros_like(S.a2pos), np.zeros_like(S.a2crd), np.zeros(S.nnz, dtype=vt))
     d_args = pk.m2(Y) if y_is_kj else pk.m2(Y, transposed_view=True)
-    fn, _, _unused = _entry(lib, _name("sddmm", sharded), S)
     fn(*pk.sparse(S), *pk.m2(X), *d_args, *pk.sparse(out))
     _lib.check()
     assert np.array_equal(out.a2pos, S.a2pos) and np.array_equal(out.a2crd, S.a2crd)
@@ -271,14 +295,15 @@ def elews_sparse_dense_to_dense(A, B, C0=None):
     return C
 
 
-def _finish_sparse_out(lib, handle, nrows, ncols, cpos, sizes):
+def _finish_sparse_out(lib, handle, nrows, ncols, cpos, sizes, vt=np.float64):
     _lib.check()
     nnz = int(sizes[8])
     dt = cpos.dtype
     ccrd = np.zeros(nnz, dtype=dt)
-    cval = np.zeros(nnz, dtype=np.float64)
+    cval = np.zeros(nnz, dtype=vt)
     pk = _Packer()
-    fn = lib.comet_b200_spgemm_numeric_f64_i32 if dt == np.int32 else lib.comet_b200_spgemm_numeric_f64_i64
+    fn = getattr(lib, "comet_b200_spgemm_numeric_%s_%s" % ("f32" if vt == np.float32 else "f64",
+                                                           "i32" if dt == np.int32 else "i64"))
     fn(handle, *pk.m1(ccrd), *pk.m1(cval))
     _lib.check()
     return SparseTensor("CSR", nrows, ncols, np.array([nrows], dtype=dt), np.array([-1], dtype=dt), cpos, ccrd,
@@ -297,7 +322,7 @@ def spgemm(A, B, M=None, semiring=PLUS_TIMES, sharded=False):
     sizes = np.zeros(13, dtype=np.int64)
     handle = fn(*pk.sparse(A), *pk.sparse(B), *pk.sparse(Mt), MASK_PUSH if M is not None else MASK_NONE,
                 _semiring(semiring), *pk.m1(cpos), *pk.m1(sizes))
-    C = _finish_sparse_out(lib, handle, A.nrows, B.ncols, cpos, sizes)
+    C = _finish_sparse_out(lib, handle, A.nrows, B.ncols, cpos, sizes, fn.value_dtype)
     if sharded:
         C.entry_offset, C.total_nnz = int(sizes[11]), int(sizes[12])
     return C

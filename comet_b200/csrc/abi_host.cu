@@ -20,6 +20,17 @@ extern "C" {
 
 namespace cb200 {
 
+// Bytes per VALUE in the host memrefs of the running entry point: 8 for the _f64_ symbols, 4 for the _f32_
+// ones (COMET instantiates both, lib/ExecutionEngine/SparseUtils.cpp:2354-2400).  float values are widened to
+// double on the device after the upload and results narrowed before the download, so both widths run the
+// same (double) kernels; a float result is the correctly rounded double result.
+static thread_local int g_vsz = 8;
+struct ValueWidth {
+    int old;
+    explicit ValueWidth(int v) : old(g_vsz) { g_vsz = v; }
+    ~ValueWidth() { g_vsz = old; }
+};
+
 struct Arr {   // a 1-D host memref
     void *data;
     int64_t n;
@@ -48,7 +59,7 @@ static int get2d(const char *what, int64_t rank, void *desc, Mat *out)
 {
     if (!desc || rank != 2) return fail("%s: expected a rank-2 memref", what);
     comet_b200_memref2d *m = (comet_b200_memref2d *)desc;
-    out->data = (double *)m->aligned + m->offset;
+    out->data = (double *)((char *)m->aligned + m->offset * (int64_t)g_vsz);
     out->rows = m->sizes[0];
     out->cols = m->sizes[1];
     out->s0 = m->strides[0];
@@ -90,7 +101,7 @@ static int get_sparse(const char *what, int isz, int32_t f1, int32_t f2, int64_t
     CB_TRY(get1d(what, r1c, p1c, isz, &a1crd));
     CB_TRY(get1d(what, r2p, p2p, isz, &a2pos));
     CB_TRY(get1d(what, r2c, p2c, isz, &a2crd));
-    CB_TRY(get1d(what, rv, pv, 8, &val));
+    CB_TRY(get1d(what, rv, pv, g_vsz, &val));
     CB_TRY(get1d(what, rd, pd, 8, &dims));
     if (dims.n < 2 || !dims.data) return fail("%s: dims memref must hold {rows, cols}", what);
     s->nrows = ((int64_t *)dims.data)[0];
@@ -179,6 +190,25 @@ struct DevBag {
         }
         return comm_allgather_inplace(cm, *p, s, st);
     }
+    // n VALUES of the entry point's width -> double on the device
+    int upload_val(double **p, const void *host, size_t n, Comm *cm = nullptr)
+    {
+        if (g_vsz == 8) return upload_rep((void **)p, host, n * 8, cm);
+        void *narrow = nullptr;
+        CB_TRY(upload_rep(&narrow, host, n * 4, cm));
+        CB_TRY(alloc((void **)p, n * 8));
+        return widen_f32_to_f64((const float *)narrow, *p, (int64_t)n, st);
+    }
+    // n doubles on the device -> VALUES of the entry point's width in the host array
+    int download_val(void *host, const double *dev, size_t n)
+    {
+        if (n == 0) return 0;
+        if (g_vsz == 8) return d2h(host, dev, n * 8, st);
+        float *narrow = nullptr;
+        CB_TRY(alloc((void **)&narrow, n * 4));
+        CB_TRY(narrow_f64_to_f32(dev, narrow, (int64_t)n, st));
+        return d2h(host, narrow, n * 4, st);
+    }
     // n indices of isz bytes -> int64 on the device (int32 input is widened there, not on the host)
     int upload_idx(int64_t **p, const void *host, int64_t n, int isz, Comm *cm = nullptr)
     {
@@ -222,7 +252,7 @@ static int upload_sparse(const char *what, const HostSparse &h, DevBag &bag, Dev
     memset(d, 0, sizeof(*d));
     cudaStream_t st = bag.st;
     CB_TRY(bag.upload_idx(&d->crd, h.a2crd, h.nnz, h.isz, rep));
-    if (need_val) CB_TRY(bag.upload_rep((void **)&d->val, h.val, (size_t)h.nnz * 8, rep));
+    if (need_val) CB_TRY(bag.upload_val(&d->val, h.val, (size_t)h.nnz, rep));
     int *flags = nullptr;                     // [0] coordinates in range, [1] COO rows ascending and in range
     CB_TRY(bag.alloc((void **)&flags, 2 * sizeof(int)));
     int got[2] = {1, 1};
@@ -289,7 +319,7 @@ static int need_stream(cudaStream_t *st)
 
 // Handles created through the host layer also own their staged operands.
 struct HostPlan {
-    int isz;
+    int isz, vsz;
     int64_t dev_handle;
     std::vector<void *> owned;
     int64_t nnz;
@@ -348,14 +378,14 @@ static int spmv_host(const HostSparse &A, Arr x, Arr y, int semiring, int accumu
     DevSparse dA;
     CB_TRY(upload_sparse("spmv", A, bag, &dA));
     double *dx, *dy;
-    CB_TRY(bag.upload((void **)&dx, x.data, (size_t)A.ncols * 8));
+    CB_TRY(bag.upload_val(&dx, x.data, (size_t)A.ncols));
     bool keep_old = accumulate || A.fmt == F_DCSR;   // rows DCSR does not store keep their value
-    if (keep_old) CB_TRY(bag.upload((void **)&dy, y.data, (size_t)A.nrows * 8));
+    if (keep_old) CB_TRY(bag.upload_val(&dy, y.data, (size_t)A.nrows));
     else CB_TRY(bag.alloc((void **)&dy, (size_t)A.nrows * 8));
     if (!accumulate && A.fmt == F_DCSR) CB_CUDA(cudaMemsetAsync(dy, 0, (size_t)A.nrows * 8, st));
     CB_TRY(comet_b200_dev_spmv_f64_i64(dA.nrows_k, A.nnz, dA.row_ids, dA.pos, dA.crd, dA.val, dx, dy,
                                        semiring, accumulate, st));
-    CB_TRY(d2h(y.data, dy, (size_t)A.nrows * 8, st));
+    CB_TRY(bag.download_val(y.data, dy, (size_t)A.nrows));
     return finish(st);
 }
 
@@ -503,19 +533,19 @@ static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiri
         // blocks of A differ from rank to rank)
         const bool big = (double)A.ncols * (double)k * 8.0 * 2.0 >= min_bytes;
         if (!accumulate && A.fmt != F_DCSR && panel >= 2 && panel % 2 == 0 && k >= 2 * panel && big &&
-            semiring == COMET_B200_PLUS_TIMES)
+            semiring == COMET_B200_PLUS_TIMES && g_vsz == 8)
             return spmm_host_panels(A, dA, bag, B, C, semiring, panel, st, cm);
     }
     double *dB, *dC;
-    CB_TRY(bag.upload_rep((void **)&dB, B.data, (size_t)((A.ncols - 1) * B.s0 + k) * 8 * (A.ncols > 0), cm));
+    CB_TRY(bag.upload_val(&dB, B.data, (size_t)((A.ncols - 1) * B.s0 + k) * (A.ncols > 0), cm));
     size_t cbytes = A.nrows > 0 ? (size_t)((A.nrows - 1) * C.s0 + k) * 8 : 0;
     bool keep_old = accumulate || A.fmt == F_DCSR || C.s0 != k;
-    if (keep_old) CB_TRY(bag.upload((void **)&dC, C.data, cbytes));
+    if (keep_old) CB_TRY(bag.upload_val(&dC, C.data, cbytes / 8));
     else CB_TRY(bag.alloc((void **)&dC, cbytes));
     if (!accumulate && A.fmt == F_DCSR) CB_CUDA(cudaMemsetAsync(dC, 0, cbytes, st));
     CB_TRY(comet_b200_dev_spmm_f64_i64(dA.nrows_k, A.ncols, A.nnz, k, dA.row_ids, dA.pos, dA.crd,
                                        dA.val, dB, B.s0, dC, C.s0, semiring, accumulate, 0, st));
-    if (cbytes) CB_TRY(d2h(C.data, dC, cbytes, st));
+    if (cbytes) CB_TRY(bag.download_val(C.data, dC, cbytes / 8));
     return finish(st);
 }
 
@@ -574,7 +604,7 @@ static void spmv_impl(int isz, COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_p
     HostSparse A;
     Arr x, y;
     if (GET_SPARSE("spmv: A", A, &A)) return;
-    if (get1d("spmv: x", x_rank, x_ptr, 8, &x) || get1d("spmv: y", y_rank, y_ptr, 8, &y)) return;
+    if (get1d("spmv: x", x_rank, x_ptr, g_vsz, &x) || get1d("spmv: y", y_rank, y_ptr, g_vsz, &y)) return;
     spmv_host(A, x, y, semiring, accumulate);
 }
 
@@ -630,15 +660,15 @@ static void sddmm_impl(int mode, COMET_B200_SPARSE2D(S), int64_t X_rank, void *X
     if (!rc) rc = sddmm_check(S, O, X, D);
     if (!rc) rc = upload_sparse("sddmm", S, bag, &dS);
     const int64_t k = rc ? 0 : X.cols;
-    if (!rc) rc = bag.upload((void **)&dX, X.data, S.nrows > 0 ? (size_t)((S.nrows - 1) * X.s0 + k) * 8 : 0);
+    if (!rc) rc = bag.upload_val(&dX, X.data, S.nrows > 0 ? (size_t)((S.nrows - 1) * X.s0 + k) : 0);
     if (guard.agree(rc)) return;
     int64_t ldy;
     if (D.s0 == 1) {                          // a row-major [cols, K] matrix viewed transposed
         ldy = D.s1;
-        if (bag.upload_rep((void **)&dY, D.data, S.ncols > 0 ? (size_t)((S.ncols - 1) * ldy + k) * 8 : 0, cm)) return;
+        if (bag.upload_val(&dY, D.data, S.ncols > 0 ? (size_t)((S.ncols - 1) * ldy + k) : 0, cm)) return;
     } else {                                  // D[k, j]: transpose on the device
         double *dD;
-        if (bag.upload_rep((void **)&dD, D.data, k > 0 ? (size_t)((k - 1) * D.s0 + S.ncols) * 8 : 0, cm)) return;
+        if (bag.upload_val(&dD, D.data, k > 0 ? (size_t)((k - 1) * D.s0 + S.ncols) : 0, cm)) return;
         ldy = k + (k & 1);
         if (bag.alloc((void **)&dY, (size_t)S.ncols * ldy * 8)) return;
         if (comet_b200_dev_transpose_f64(k, S.ncols, dD, D.s0, dY, ldy, st)) return;
@@ -646,7 +676,7 @@ static void sddmm_impl(int mode, COMET_B200_SPARSE2D(S), int64_t X_rank, void *X
     if (bag.alloc((void **)&dOut, (size_t)S.nnz * 8)) return;
     if (comet_b200_dev_sddmm_f64_i64(S.nrows, S.nnz, k, dS.pos, dS.crd, dS.val, dX, X.s0, dY, ldy, dOut, st))
         return;
-    if (S.nnz && d2h(O.val, dOut, (size_t)S.nnz * 8, st)) return;
+    if (bag.download_val(O.val, dOut, (size_t)S.nnz)) return;
     copy_pattern(S, O);
     finish(st);
 }
@@ -949,6 +979,7 @@ static int64_t sparse_out_symbolic(int isz, int kind, const HostSparse &A, const
     hp->dev_handle = dev_handle;
     hp->nnz = nnz;
     hp->isz = isz;
+    hp->vsz = g_vsz;
     hp->owned.swap(bag.ptrs);   // staged operands live until the numeric call
     std::lock_guard<std::mutex> lk(g_hp_mu);
     g_hplans[dev_handle] = hp;
@@ -1009,8 +1040,9 @@ static void spgemm_numeric_impl(int isz, int64_t handle, int64_t C2crd_rank, voi
     if (!hp) { fail("numeric phase: unknown handle %lld", (long long)handle); return; }
     cudaStream_t st = lib_stream();
     Arr crd, val;
-    int rc = get1d("C2crd", C2crd_rank, C2crd_ptr, isz, &crd) || get1d("Cval", Cval_rank, Cval_ptr, 8, &val);
-    if (!rc && hp->isz != isz) rc = fail("numeric phase: the handle was created by the entry point of the other index width");
+    int rc = get1d("C2crd", C2crd_rank, C2crd_ptr, isz, &crd) || get1d("Cval", Cval_rank, Cval_ptr, g_vsz, &val);
+    if (!rc && (hp->isz != isz || hp->vsz != g_vsz))
+        rc = fail("numeric phase: the handle was created by the entry point of another index or value width");
     if (!rc && (crd.n < hp->nnz || val.n < hp->nnz)) rc = fail("numeric phase: C2crd/Cval shorter than nnz");
     int64_t *dcrd = nullptr;
     double *dval = nullptr;
@@ -1026,14 +1058,21 @@ static void spgemm_numeric_impl(int isz, int64_t handle, int64_t C2crd_rank, voi
             rc = fail("numeric phase: device allocation failed");
         if (!rc) rc = narrow_any_i64_to_i32(dcrd, dcrd32, hp->nnz, st);
     }
+    float *dval32 = nullptr;
+    if (!rc && hp->nnz && g_vsz == 4) {
+        if (cudaMallocAsync((void **)&dval32, (size_t)hp->nnz * 4, st) != cudaSuccess)
+            rc = fail("numeric phase: device allocation failed");
+        if (!rc) rc = narrow_f64_to_f32(dval, dval32, hp->nnz, st);
+    }
     if (!rc && hp->nnz) {
         if (d2h(crd.data, isz == 4 ? (void *)dcrd32 : (void *)dcrd, (size_t)hp->nnz * isz, st) ||
-            d2h(val.data, dval, (size_t)hp->nnz * 8, st))
+            d2h(val.data, g_vsz == 4 ? (void *)dval32 : (void *)dval, (size_t)hp->nnz * g_vsz, st))
             rc = 1;
     }
     if (finish(st) && !rc) fail("numeric phase: synchronize failed");
     if (dcrd) cudaFreeAsync(dcrd, st);
     if (dcrd32) cudaFreeAsync(dcrd32, st);
+    if (dval32) cudaFreeAsync(dval32, st);
     if (dval) cudaFreeAsync(dval, st);
     for (void *p : hp->owned) cudaFreeAsync(p, st);
     delete hp;
@@ -1141,6 +1180,32 @@ BOTH_WIDTHS(void, masked_spgemm_count, masked_count_impl,
             (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
              int64_t out_rank, void *out_ptr),
             FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, out_rank, out_ptr)
+
+// float values (COMET instantiates _f32_ runtime symbols next to the _f64_ ones,
+// lib/ExecutionEngine/SparseUtils.cpp:2354-2400): same implementations with 4-byte values in the host memrefs.
+#define F32_WIDTHS(RET, NAME, IMPL, PARAMS, ...)                                                    \
+    RET comet_b200_##NAME##_f32_i64 PARAMS { ValueWidth w_(4); return IMPL(8, __VA_ARGS__); }       \
+    RET comet_b200_##NAME##_f32_i32 PARAMS { ValueWidth w_(4); return IMPL(4, __VA_ARGS__); }
+
+F32_WIDTHS(void, spmv, spmv_impl,
+           (COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr, int64_t y_rank, void *y_ptr, int32_t semiring,
+            int32_t accumulate),
+           FWD_SPARSE(A), x_rank, x_ptr, y_rank, y_ptr, semiring, accumulate)
+F32_WIDTHS(void, spmm, spmm_impl,
+           (COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr, int64_t C_rank, void *C_ptr, int32_t semiring,
+            int32_t accumulate),
+           FWD_SPARSE(A), B_rank, B_ptr, C_rank, C_ptr, semiring, accumulate)
+F32_WIDTHS(void, sddmm, sddmm_impl,
+           (COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr, int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O)),
+           FWD_SPARSE(S), X_rank, X_ptr, D_rank, D_ptr, FWD_SPARSE(O))
+F32_WIDTHS(int64_t, spgemm_symbolic, spgemm_symbolic_impl,
+           (COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type, int32_t semiring,
+            int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr),
+           FWD_SPARSE(A), FWD_SPARSE(B), FWD_SPARSE(M), mask_type, semiring, C2pos_rank,
+           C2pos_ptr, sizes_rank, sizes_ptr)
+F32_WIDTHS(void, spgemm_numeric, spgemm_numeric_impl,
+           (int64_t handle, int64_t C2crd_rank, void *C2crd_ptr, int64_t Cval_rank, void *Cval_ptr),
+           handle, C2crd_rank, C2crd_ptr, Cval_rank, Cval_ptr)
 
 // The same operations on one row block per rank, under the communicator of comet_b200_comm_init.
 #define SHARDED_WIDTHS(RET, NAME, IMPL, PARAMS, ...)                                              \

@@ -72,6 +72,8 @@ cudaStream_t aux_stream(int i);   // two more streams (i = 0, 1) for copies that
 int narrow_i64_to_i32(const int64_t *src, int32_t *dst, int64_t n, cudaStream_t st);
 int narrow_any_i64_to_i32(const int64_t *src, int32_t *dst, int64_t n, cudaStream_t st);
 int widen_i32_to_i64(const int32_t *src, int64_t *dst, int64_t n, cudaStream_t st);
+int widen_f32_to_f64(const float *src, double *dst, int64_t n, cudaStream_t st);
+int narrow_f64_to_f32(const double *src, float *dst, int64_t n, cudaStream_t st);
 // out[0..n] = exclusive prefix sum of in[0..n-1], out[n] = total
 int exclusive_scan_i64(const int64_t *in, int64_t *out, int64_t n, cudaStream_t st);
 // sorted COO row coordinates -> row pointer; *sorted_flag_dev set to 0 if rows are not ascending

@@ -36,11 +36,41 @@ __global__ void __launch_bounds__(256) narrow_scalar_kernel(const int64_t *__res
         dst[i] = (int32_t)src[i];
 }
 
+// float <-> double copies for the _f32_ entry points (values are widened once after the upload and results
+// narrowed once before the download; every kernel computes in double)
+__global__ void __launch_bounds__(256) widen_f32_kernel(const float *__restrict__ src, double *__restrict__ dst, int64_t n)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = (double)__ldcs(src + i);
+}
+
+__global__ void __launch_bounds__(256) narrow_f64_kernel(const double *__restrict__ src, float *__restrict__ dst, int64_t n)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = (float)__ldcs(src + i);
+}
+
 static unsigned stream_grid(int64_t n)
 {
     int64_t blocks = ceil_div(n, 256);
     int64_t cap = (int64_t)sm_count() * 16;
     return (unsigned)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
+}
+
+int widen_f32_to_f64(const float *src, double *dst, int64_t n, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    widen_f32_kernel<<<stream_grid(n), 256, 0, st>>>(src, dst, n);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+int narrow_f64_to_f32(const double *src, float *dst, int64_t n, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    narrow_f64_kernel<<<stream_grid(n), 256, 0, st>>>(src, dst, n);
+    CB_LAUNCH_CHECK();
+    return 0;
 }
 
 int widen_i32_to_i64(const int32_t *src, int64_t *dst, int64_t n, cudaStream_t st)

@@ -302,6 +302,41 @@ COMET_B200_EXPORT void comet_b200_masked_spgemm_count_f64_i32(
     int32_t semiring, int64_t out_rank, void *out_ptr);
 
 /* ------------------------------------------------------------------------- */
+/* float values: COMET instantiates its runtime symbols for f32 as well        */
+/* (read_input_2D_f32_i32 / _f32_i64, lib/ExecutionEngine/SparseUtils.cpp      */
+/* :2354-2400).  Same argument lists; value memrefs (vals, x, y, B, C, X, D)   */
+/* hold float.  Values are widened to double on the device after the upload    */
+/* and results rounded to float once before the download, so a result equals   */
+/* the double-precision result rounded to float.                               */
+/* ------------------------------------------------------------------------- */
+COMET_B200_EXPORT void comet_b200_spmv_f32_i64(COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr,
+                                               int64_t y_rank, void *y_ptr, int32_t semiring,
+                                               int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_spmv_f32_i32(COMET_B200_SPARSE2D(A), int64_t x_rank, void *x_ptr,
+                                               int64_t y_rank, void *y_ptr, int32_t semiring,
+                                               int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_spmm_f32_i64(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                                               int64_t C_rank, void *C_ptr, int32_t semiring,
+                                               int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_spmm_f32_i32(COMET_B200_SPARSE2D(A), int64_t B_rank, void *B_ptr,
+                                               int64_t C_rank, void *C_ptr, int32_t semiring,
+                                               int32_t accumulate);
+COMET_B200_EXPORT void comet_b200_sddmm_f32_i64(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr,
+                                                int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O));
+COMET_B200_EXPORT void comet_b200_sddmm_f32_i32(COMET_B200_SPARSE2D(S), int64_t X_rank, void *X_ptr,
+                                                int64_t D_rank, void *D_ptr, COMET_B200_SPARSE2D(O));
+COMET_B200_EXPORT int64_t comet_b200_spgemm_symbolic_f32_i64(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr);
+COMET_B200_EXPORT int64_t comet_b200_spgemm_symbolic_f32_i32(
+    COMET_B200_SPARSE2D(A), COMET_B200_SPARSE2D(B), COMET_B200_SPARSE2D(M), int32_t mask_type,
+    int32_t semiring, int64_t C2pos_rank, void *C2pos_ptr, int64_t sizes_rank, void *sizes_ptr);
+COMET_B200_EXPORT void comet_b200_spgemm_numeric_f32_i64(int64_t handle, int64_t C2crd_rank, void *C2crd_ptr,
+                                                         int64_t Cval_rank, void *Cval_ptr);
+COMET_B200_EXPORT void comet_b200_spgemm_numeric_f32_i32(int64_t handle, int64_t C2crd_rank, void *C2crd_ptr,
+                                                         int64_t Cval_rank, void *Cval_ptr);
+
+/* ------------------------------------------------------------------------- */
 /* Several GPUs: one process per GPU, one row block of the left operand per    */
 /* rank.  COMET itself has no collective and no multi-device runtime (its      */
 /* generated code calls the runtime from one host thread,                      */

@@ -35,6 +35,13 @@
 
 #define ORACLE_API __attribute__((visibility("default")))
 
+/* Single-precision build (-DORACLE_F32 -> libcomet_oracle_f32.so): COMET generates the same loops for
+   Tensor<float>, with f32 mulf / addf.  Every `double` from here on becomes float, so the arithmetic below
+   is done in single precision in the same order; the system headers above keep their own double. */
+#ifdef ORACLE_F32
+#define double float
+#endif
+
 /* semiring codes shared with include/comet_b200.h */
 enum { SEMIRING_PLUS_TIMES = 0, SEMIRING_PLUS_PAIR = 1, SEMIRING_PLUS_FIRST = 2, SEMIRING_PLUS_SECOND = 3,
        SEMIRING_MIN_PLUS = 4, SEMIRING_MIN_FIRST = 5, SEMIRING_MIN_SECOND = 6, SEMIRING_ANY_PAIR = 7 };

@@ -23,15 +23,18 @@ PLUS_TIMES, PLUS_PAIR, PLUS_FIRST, PLUS_SECOND, MIN_PLUS, MIN_FIRST, MIN_SECOND,
 DENSE, CU, CN, S = 0, 1, 2, 3
 FORMATS = {"CSR": (DENSE, CU), "DCSR": (CU, CU), "COO": (CN, S)}
 
+_LIB32_PATH = os.path.join(_HERE, "libcomet_oracle_f32.so")   # the same loops with float values
+
 _lib = None
+_lib32 = None
 
 
 def build(force=False):
     """Compile the oracle with gcc (no GPU needed)."""
     src = os.path.join(_HERE, "comet_oracle.c")
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
-        subprocess.check_call(["make", "-C", _HERE, "-B", "libcomet_oracle.so"],
-                              stdout=subprocess.DEVNULL)
+    stale = lambda p: not os.path.exists(p) or os.path.getmtime(p) < os.path.getmtime(src)
+    if force or stale(_LIB_PATH) or stale(_LIB32_PATH):
+        subprocess.check_call(["make", "-C", _HERE, "-B", "all"], stdout=subprocess.DEVNULL)
     return _LIB_PATH
 
 
@@ -333,3 +336,59 @@ def print_memref(a):
     else:
         body = "".join("%g," % float(v) for v in a)
     return "data = \n" + body + "\n"
+
+
+# --- single precision: the same loop nests compiled with float values (libcomet_oracle_f32.so) -----------
+
+def lib32():
+    global _lib32
+    if _lib32 is None:
+        if not os.path.exists(_LIB32_PATH):
+            build(force=True)
+        _lib32 = ctypes.CDLL(_LIB32_PATH)
+        _lib32.oracle_spgemm_symbolic.restype = ctypes.c_int64
+    return _lib32
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def spmv_f32(A, x):
+    x = _f32(x)
+    y = np.zeros(A.nrows, dtype=np.float32)
+    lib32().oracle_spmv_csr(_l(A.nrows), _p(_i64(A.a2pos)), _p(_i64(A.a2crd)), _p(_f32(A.val)), _p(x), _p(y), 0)
+    return y
+
+
+def spmm_f32(A, B):
+    B = _f32(B)
+    k = B.shape[1]
+    C = np.zeros((A.nrows, k), dtype=np.float32)
+    lib32().oracle_spmm_csr(_l(A.nrows), _l(k), _p(_i64(A.a2pos)), _p(_i64(A.a2crd)), _p(_f32(A.val)), _p(B),
+                            _l(k), _p(C), _l(k), 0)
+    return C
+
+
+def sddmm_f32(S, X, Y):
+    X, Y = _f32(X), _f32(Y)
+    k = X.shape[1]
+    out = np.zeros(S.nnz, dtype=np.float32)
+    lib32().oracle_sddmm_csr(_l(S.nrows), _l(k), _p(_i64(S.a2pos)), _p(_i64(S.a2crd)), _p(_f32(S.val)), _p(X),
+                             _l(k), _p(Y), _l(1), _l(k), _p(out))
+    return out
+
+
+def spgemm_f32(A, B):
+    L = lib32()
+    apos, acrd, aval = _i64(A.a2pos), _i64(A.a2crd), _f32(A.val)
+    bpos, bcrd, bval = _i64(B.a2pos), _i64(B.a2crd), _f32(B.val)
+    cpos = np.zeros(A.nrows + 1, dtype=np.int64)
+    nnz = L.oracle_spgemm_symbolic(_l(A.nrows), _l(B.ncols), _p(apos), _p(acrd), _p(bpos), _p(bcrd), None, None,
+                                   _p(cpos))
+    ccrd = np.zeros(max(nnz, 1), dtype=np.int64)
+    cval = np.zeros(max(nnz, 1), dtype=np.float32)
+    L.oracle_spgemm_numeric(_l(A.nrows), _l(B.ncols), _p(apos), _p(acrd), _p(aval), _p(bpos), _p(bcrd), _p(bval),
+                            None, None, 0, _p(cpos), _p(ccrd), _p(cval))
+    return SparseArrays("CSR", A.nrows, B.ncols, np.array([A.nrows], dtype=np.int64),
+                        np.array([-1], dtype=np.int64), cpos, ccrd[:nnz], cval[:nnz])
