@@ -212,6 +212,12 @@ class Workload:
     def cpu_alt(self):
         return None
 
+    def e2e_weights(self):
+        """Per-row bytes that cross PCIe in the end-to-end call (None: keep the kernel-balanced blocks).
+        Through the host entry points the transfer, not the kernel, is what a rank spends its time on, so
+        the host program cuts its row blocks for equal bytes there."""
+        return None
+
 
 class SpMM(Workload):
     name = "spmm"
@@ -241,6 +247,9 @@ class SpMM(Workload):
 
     def step(self, dev):
         dev.spmm(self.dA, self.dB, self.dC, variant=self.args.variant)
+
+    def e2e_weights(self):
+        return 16.0 * np.diff(self.A.a2pos) + 8.0 * self.k + 8.0      # the row's entries up, its row of C down
 
     def check(self, torch, dev):
         from oracle import oracle
@@ -386,6 +395,9 @@ class SDDMM(Workload):
 
     def step(self, dev):
         dev.sddmm(self.dA, self.dX, self.dY, self.dout)
+
+    def e2e_weights(self):
+        return 24.0 * np.diff(self.A.a2pos) + 8.0 * self.k + 8.0      # entries up, values down, the row of X up
 
     def _check_vals(self, vals, seed):
         from oracle import oracle
@@ -835,9 +847,14 @@ def measure(w, args, env, headline):
 
     # parity of this rank's block against the CPU oracle (outside every timed region)
     ok = bool(w.check(torch, dev))
+    kernel_bounds = list(w.bounds)
 
     # end to end through the host-memref entry points: pinned buffers, then plain ones
     e2e = {}
+    e2e_bounds = None
+    if not args.kernel_only and world > 1 and w.e2e_weights() is not None:
+        e2e_bounds = sharding.row_blocks(w.A.a2pos, world, weights=w.e2e_weights())
+        w.place(e2e_bounds, torch, dev, sharding)
     if not args.kernel_only:
         for key, pinned in (("e2e", True), ("e2e_pageable", False)):
             h2d, d2h = w.e2e_setup(torch, pinned)
@@ -886,7 +903,10 @@ def measure(w, args, env, headline):
     }
     if world > 1:
         res["rebalance_per_rank_ms"] = history
-        res["row_bounds"] = [int(b) for b in w.bounds]
+        res["row_bounds"] = [int(b) for b in kernel_bounds]
+        if e2e_bounds is not None:
+            res["e2e_row_bounds"] = [int(b) for b in e2e_bounds]
+            res["e2e_row_bounds_note"] = "the end-to-end leg cuts rows for equal bytes over PCIe, the kernel leg for equal kernel time"
     res.update(e2e)
     if "probes" in w.__dict__:
         res["probes_per_s"] = w.probes / (ms_per_step * 1e-3)
@@ -1021,7 +1041,8 @@ def main():
             "clocks": clocks,
         }
         for key in ("e2e", "e2e_pageable", "gpu_launches", "roofline", "per_rank_kernel_ms", "parity_checked",
-                    "cpu_baseline", "rebalance_per_rank_ms", "row_bounds", "probes_per_s", "nnz_c"):
+                    "cpu_baseline", "rebalance_per_rank_ms", "row_bounds", "e2e_row_bounds", "e2e_row_bounds_note",
+                    "probes_per_s", "nnz_c"):
             if key in head:
                 line[key] = head[key]
         if others:

@@ -532,8 +532,15 @@ static int spmm_host(const HostSparse &A, const Mat &B, const Mat &C, int semiri
         // (decided from B alone: under a communicator every rank must take the same branch, and the
         // blocks of A differ from rank to rank)
         const bool big = (double)A.ncols * (double)k * 8.0 * 2.0 >= min_bytes;
+        // Pageable host matrices are moved by the staged copier, whose worker threads would have to copy
+        // panel rows of a few hundred bytes each out of / into the wide rows: measured slower than one
+        // contiguous upload and one contiguous download (46 against 93 ms on two GPUs), so the panels are
+        // kept for page-locked operands.  (Every rank decides from its own pointers; ranks that mix pinned
+        // and pageable operands must force one mode with COMET_B200_SPMM_PANEL, since the all-gather of the
+        // two paths differs.)
+        const bool pinned = env || (!host_is_pageable(B.data) && !host_is_pageable(C.data));
         if (!accumulate && A.fmt != F_DCSR && panel >= 2 && panel % 2 == 0 && k >= 2 * panel && big &&
-            semiring == COMET_B200_PLUS_TIMES && g_vsz == 8)
+            semiring == COMET_B200_PLUS_TIMES && g_vsz == 8 && pinned)
             return spmm_host_panels(A, dA, bag, B, C, semiring, panel, st, cm);
     }
     double *dB, *dC;

@@ -53,7 +53,7 @@ void set1d(M1 *m, void *data, int64_t n)
 
 void *zalloc(size_t bytes)
 {
-    void *p = malloc(bytes ? bytes : 8);
+    void *p = calloc(bytes ? bytes : 8, 1);     // zeroed: an output's row pointer is read as "no entries yet" by layer 1
     if (!p) {
         fail("ciface: out of host memory (%zu bytes)", bytes);
         return nullptr;

@@ -5,16 +5,145 @@
 // std::stable_sort by (row, col) and keeps duplicates (lib/ExecutionEngine/SparseUtils.cpp:360-367,
 // 404-533), and transpose_2D turns CSR into coordinates, sorts them by (col, row) and rebuilds the
 // row pointer (lib/ExecutionEngine/TransposeUtils.cpp:738-812).  Here both are one radix sort of
-// 64-bit keys major * extent + minor carrying the entry's position (CUB's device radix sort: least
-// significant digit first, stable, so equal coordinates keep their input order like stable_sort),
-// a gather of the values, and the row pointer from the sorted majors.
+// 64-bit keys major * extent + minor carrying the entry's position (least significant digit first,
+// stable, so equal coordinates keep their input order like stable_sort), a gather of the values, and
+// the row pointer from the sorted majors.
 //
-// Bound: HBM (a radix sort pass reads and writes 16 bytes per entry; passes = key bits / 8).
-#include <cub/device/device_radix_sort.cuh>
-
+// The sort is this file's own: per 8-bit digit, a counting kernel (digit histogram per tile), one
+// exclusive scan over the digit-major table of counts, and a scatter kernel that ranks every key
+// inside its tile.  Ranking is what makes it stable: a warp walks its part of the tile 32
+// consecutive keys at a time, `__match_any_sync` names the lanes that hold the same digit, a key's
+// rank is the number of such lanes below it plus the count its warp has already seen for the digit,
+// and warps are ordered by a prefix over their counts.
+//
+// Bound: HBM (a pass reads 32 and writes 16 bytes per entry; passes = key bits / 8).
 #include "common.cuh"
 
 namespace cb200 {
+
+// ---------------------------------------------------------------------------
+// Stable LSD radix sort of (uint64 key, int64 payload) pairs.
+// ---------------------------------------------------------------------------
+static const int RS_THREADS = 256;                    // 8 warps
+static const int RS_ROUNDS = 16;                      // rounds of 32 keys per warp
+static const int RS_TILE = RS_THREADS * RS_ROUNDS;    // keys per CTA
+static const int RS_DIGITS = 256;
+
+// Walks this warp's part of the tile in order.  On return cnt[d] (this warp's row of shared counters) holds
+// the number of keys with digit d, and offs[r] the rank of the key of round r among the warp's keys with the
+// same digit.  SCATTER = false only counts.
+template <bool SCATTER>
+__device__ __forceinline__ void rs_rank_warp(const uint64_t *__restrict__ keys, int64_t base, int64_t n, int shift,
+                                             unsigned *cnt, uint64_t (&k)[RS_ROUNDS], unsigned (&offs)[RS_ROUNDS])
+{
+    const int lane = threadIdx.x & 31;
+    const unsigned below = (1u << lane) - 1u;
+#pragma unroll
+    for (int r = 0; r < RS_ROUNDS; r++) {
+        const int64_t i = base + r * 32 + lane;
+        const bool live = i < n;
+        const uint64_t key = live ? keys[i] : 0;
+        const unsigned d = live ? (unsigned)((key >> shift) & (RS_DIGITS - 1)) : RS_DIGITS;   // dead lanes form their own group
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        const int leader = __ffs(peers) - 1;
+        unsigned old = 0;
+        if (live && lane == leader) {
+            old = cnt[d];
+            cnt[d] = old + __popc(peers);
+        }
+        old = __shfl_sync(0xffffffffu, old, leader);
+        __syncwarp();
+        if (SCATTER) {
+            k[r] = key;
+            offs[r] = old + __popc(peers & below);
+        }
+    }
+}
+
+// hist[d * ntiles + tile] = number of keys of the tile with digit d
+__global__ void __launch_bounds__(RS_THREADS)
+rs_count_kernel(const uint64_t *__restrict__ keys, int64_t n, int shift, int64_t ntiles, int64_t *__restrict__ hist)
+{
+    __shared__ unsigned cnt[RS_THREADS / 32][RS_DIGITS];
+    const int w = threadIdx.x >> 5;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        for (int i = threadIdx.x; i < (RS_THREADS / 32) * RS_DIGITS; i += RS_THREADS) (&cnt[0][0])[i] = 0;
+        __syncthreads();
+        uint64_t k[RS_ROUNDS];
+        unsigned offs[RS_ROUNDS];
+        rs_rank_warp<false>(keys, tile * RS_TILE + (int64_t)w * 32 * RS_ROUNDS, n, shift, cnt[w], k, offs);
+        __syncthreads();
+        if (threadIdx.x < RS_DIGITS) {
+            unsigned t = 0;
+            for (int i = 0; i < RS_THREADS / 32; i++) t += cnt[i][threadIdx.x];
+            hist[(int64_t)threadIdx.x * ntiles + tile] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// base[d * ntiles + tile] = first output position of the tile's keys with digit d (exclusive scan of hist)
+__global__ void __launch_bounds__(RS_THREADS)
+rs_scatter_kernel(const uint64_t *__restrict__ keys, const int64_t *__restrict__ vals, int64_t n, int shift,
+                  int64_t ntiles, const int64_t *__restrict__ base, uint64_t *__restrict__ keys_out,
+                  int64_t *__restrict__ vals_out)
+{
+    __shared__ unsigned cnt[RS_THREADS / 32][RS_DIGITS];
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        for (int i = threadIdx.x; i < (RS_THREADS / 32) * RS_DIGITS; i += RS_THREADS) (&cnt[0][0])[i] = 0;
+        __syncthreads();
+        uint64_t k[RS_ROUNDS];
+        unsigned offs[RS_ROUNDS];
+        const int64_t wbase = tile * RS_TILE + (int64_t)w * 32 * RS_ROUNDS;
+        rs_rank_warp<true>(keys, wbase, n, shift, cnt[w], k, offs);
+        __syncthreads();
+        if (threadIdx.x < RS_DIGITS) {        // counts per warp -> start of each warp's keys inside the tile's run of the digit
+            unsigned run = 0;
+            for (int i = 0; i < RS_THREADS / 32; i++) {
+                const unsigned c = cnt[i][threadIdx.x];
+                cnt[i][threadIdx.x] = run;
+                run += c;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < RS_ROUNDS; r++) {
+            const int64_t i = wbase + r * 32 + lane;
+            if (i < n) {
+                const unsigned d = (unsigned)((k[r] >> shift) & (RS_DIGITS - 1));
+                const int64_t at = base[(int64_t)d * ntiles + tile] + cnt[w][d] + offs[r];
+                keys_out[at] = k[r];
+                vals_out[at] = vals[i];
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Sorts n pairs by the low `bits` bits of the key.  The result is in (keys, vals) or (keys2, vals2): *in_second
+// tells which.  hist / base: scratch of 256 * ntiles + 1 int64 each.
+static int radix_sort_pairs(uint64_t *keys, uint64_t *keys2, int64_t *vals, int64_t *vals2, int64_t n, int bits,
+                            int64_t *hist, int64_t *base, bool *in_second, cudaStream_t st)
+{
+    const int64_t ntiles = ceil_div(n, RS_TILE);
+    int64_t grid = ntiles;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (grid > cap) grid = cap;
+    bool second = false;
+    for (int shift = 0; shift < bits; shift += 8) {
+        uint64_t *kin = second ? keys2 : keys, *kout = second ? keys : keys2;
+        int64_t *vin = second ? vals2 : vals, *vout = second ? vals : vals2;
+        rs_count_kernel<<<(unsigned)grid, RS_THREADS, 0, st>>>(kin, n, shift, ntiles, hist);
+        CB_LAUNCH_CHECK();
+        CB_TRY(exclusive_scan_i64(hist, base, RS_DIGITS * ntiles, st));
+        rs_scatter_kernel<<<(unsigned)grid, RS_THREADS, 0, st>>>(kin, vin, n, shift, ntiles, base, kout, vout);
+        CB_LAUNCH_CHECK();
+        second = !second;
+    }
+    *in_second = second;
+    return 0;
+}
 
 __global__ void __launch_bounds__(256)
 make_keys_kernel(int64_t n, const int64_t *__restrict__ major, const int64_t *__restrict__ minor,
@@ -84,10 +213,9 @@ int sort_coo(int64_t n, int64_t nmajor, int64_t nminor, const int64_t *major, co
     int bits = 0;
     CB_TRY(key_bits(nmajor, nminor, &bits));
     uint64_t *keys = nullptr, *keys2 = nullptr;
-    int64_t *idx = nullptr, *idx2 = nullptr;
+    int64_t *idx = nullptr, *idx2 = nullptr, *hist = nullptr, *base = nullptr;
     int *bad = nullptr;
-    void *tmp = nullptr;
-    size_t tmp_bytes = 0;
+    const size_t table = (size_t)RS_DIGITS * (size_t)ceil_div(n, RS_TILE) + 1;
     int rc = 0;
     auto alloc = [&](void **p, size_t bytes) {
         if (rc) return;
@@ -101,26 +229,25 @@ int sort_coo(int64_t n, int64_t nmajor, int64_t nminor, const int64_t *major, co
     alloc((void **)&idx, (size_t)n * 8);
     alloc((void **)&idx2, (size_t)n * 8);
     alloc((void **)&bad, sizeof(int));
-    if (!rc && cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, keys, keys2, idx, idx2, n, 0, bits, st) != cudaSuccess)
-        rc = fail("sort: size query failed");
-    alloc(&tmp, tmp_bytes);
+    alloc((void **)&hist, table * 8);
+    alloc((void **)&base, table * 8);
     int bad_host = 0;
+    bool second = false;
     if (!rc) {
         cudaMemsetAsync(bad, 0, sizeof(int), st);
         make_keys_kernel<<<grid_for(n), 256, 0, st>>>(n, major, minor, nmajor, nminor, keys, idx, bad);
-        if (cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, keys, keys2, idx, idx2, n, 0, bits, st) != cudaSuccess)
-            rc = fail("sort: radix sort failed");
+        rc = radix_sort_pairs(keys, keys2, idx, idx2, n, bits, hist, base, &second, st);
     }
     if (!rc) {
-        gather_sorted_kernel<<<grid_for(n), 256, 0, st>>>(n, keys2, idx2, nminor, vals, major_out, minor_out,
-                                                          vals ? vals_out : nullptr);
+        gather_sorted_kernel<<<grid_for(n), 256, 0, st>>>(n, second ? keys2 : keys, second ? idx2 : idx, nminor, vals,
+                                                          major_out, minor_out, vals ? vals_out : nullptr);
         if (cudaMemcpyAsync(&bad_host, bad, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
             cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess)
             rc = fail("sort: kernels failed");
         else if (bad_host)
             rc = fail("sort: a coordinate lies outside %lld x %lld", (long long)nmajor, (long long)nminor);
     }
-    void *all[] = {keys, keys2, idx, idx2, bad, tmp};
+    void *all[] = {keys, keys2, idx, idx2, bad, hist, base};
     for (void *p : all)
         if (p) cudaFreeAsync(p, st);
     return rc;

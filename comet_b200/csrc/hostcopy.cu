@@ -49,11 +49,16 @@ class Pool {
   public:
     explicit Pool(int device) : device_(device)
     {
-        int n = (int)std::thread::hardware_concurrency() / 4;
+        // half of the cores this process can count on: launchers that start one process per GPU export
+        // LOCAL_WORLD_SIZE, and the processes of one node share its cores
+        int share = 1;
+        const char *lws = getenv("LOCAL_WORLD_SIZE");
+        if (lws && atoi(lws) > 1) share = atoi(lws);
+        int n = (int)std::thread::hardware_concurrency() / (2 * share);
         const char *env = getenv("COMET_B200_COPY_THREADS");
         if (env) n = atoi(env);
         if (n < 2) n = 2;
-        if (n > 8) n = 8;
+        if (n > 12) n = 12;
         for (int i = 0; i < SLOTS; i++) {
             Slot s;
             if (cudaHostAlloc((void **)&s.buf, CHUNK, cudaHostAllocDefault) != cudaSuccess) break;

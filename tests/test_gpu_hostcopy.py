@@ -47,6 +47,8 @@ def test_spmm_through_pageable_host_arrays(monkeypatch, mode, panels):
     if mode == "driver":
         monkeypatch.setenv("COMET_B200_STAGED_COPIES", "0")
     monkeypatch.setenv("COMET_B200_SPMM_PANEL_MIN_BYTES", "0" if panels else "1e18")
+    if panels:
+        monkeypatch.setenv("COMET_B200_SPMM_PANEL", "32")       # asked for by name: kept even for pageable operands
     _spmm_window(A, wide, 5, k, out, 3)
     B = np.ascontiguousarray(wide[:, 5:5 + k])
     _close(out[:, 3:3 + k], oracle.spmm(_orc(A), B), oracle.spmm(_orc(A, True), np.abs(B)))
