@@ -6,8 +6,9 @@
 // mirror, a missing value reads as 1.0, `array` files list a dense matrix column by column), sorts them
 // with std::stable_sort by (row, col) without merging duplicates (:360-367), and fills CSR / DCSR / COO
 // arrays, for CSR and COO through the triangular filter of the read mode (:462-520, :1859-1893).
-// Here the text is parsed on the host, the coordinates are sorted on the device (convert.cu), and the
-// linear fill runs on the host again over the sorted entries.  A parsed and sorted file is kept per path,
+// Here the host reads the file and parses only the banner and the size line; the entry lines are parsed
+// (parse.cu) and the coordinates sorted (convert.cu) on the device, and the linear fill of the caller's
+// arrays runs on the host over the sorted entries.  A parsed and sorted file is kept per path,
 // as the reference keeps its FileReaderWrapper per file id, so the sizes call and the fill call that
 // follows share one parse and one sort.
 #include <stdio.h>
@@ -35,6 +36,10 @@ struct SortedFile {
 static std::mutex g_files_mu;
 static std::map<std::string, SortedFile *> g_files;
 
+int parse_market_body_on_device(const char *path, const char *body, int64_t nbytes, bool array, bool symmetric,
+                                bool skew, int64_t nrows, int64_t ncols, int64_t capacity, int64_t **drow,
+                                int64_t **dcol, double **dval, int64_t *count, cudaStream_t st);
+
 static bool blank(const char *s, const char *e)
 {
     for (; s < e; s++)
@@ -42,89 +47,55 @@ static bool blank(const char *s, const char *e)
     return true;
 }
 
-static int parse_market(const std::string &path, SortedFile *m)
+struct MarketHeader {
+    bool symmetric = false, skew = false, array = false;
+    int64_t nrows = 0, ncols = 0, capacity = 0;     // capacity: entries the size line allows (doubled for symmetric files)
+    size_t body = 0;                                // offset of the first byte after the size line
+};
+
+// Banner, comments and the size line: the only part of the file the host parses.
+static int parse_header(const std::string &path, const std::string &text, MarketHeader *h)
 {
-    FILE *f = fopen(path.c_str(), "rb");
-    if (!f) return fail("reader: cannot open %s", path.c_str());
-    std::string text;
-    char buf[1 << 16];
-    size_t got;
-    while ((got = fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, got);
-    fclose(f);
-    bool symmetric = false, skew = false, array = false, have_size = false;
-    int64_t cap = 0, seen = 0;
     const char *p = text.data(), *end = p + text.size();
     while (p < end) {
         const char *nl = (const char *)memchr(p, '\n', (size_t)(end - p));
         const char *le = nl ? nl : end;
+        const char *next = nl ? nl + 1 : end;
         if (*p == '%') {
             if (p + 1 < le && p[1] == '%') {
                 const std::string banner(p, le);
-                symmetric = banner.find("symmetric") != std::string::npos;
-                skew = banner.find("skew") != std::string::npos;
-                array = banner.find("array") != std::string::npos;
+                h->symmetric = banner.find("symmetric") != std::string::npos;
+                h->skew = banner.find("skew") != std::string::npos;
+                h->array = banner.find("array") != std::string::npos;
             }
         } else if (!blank(p, le)) {
-            std::string line(p, le);                    // NUL-terminated copy for strtol / strtod
+            std::string line(p, le);                    // NUL-terminated copy for strtoll
             char *l = &line[0], *t = nullptr;
-            if (!have_size) {
-                long long a = strtoll(l, &t, 10);
-                if (t == l) return fail("reader: %s: bad size line", path.c_str());
-                l = t;
-                long long b = strtoll(l, &t, 10);
-                if (t == l) return fail("reader: %s: bad size line", path.c_str());
-                l = t;
-                long long c = strtoll(l, &t, 10);
-                if (array) {
-                    cap = a * b;
-                } else {
-                    if (t == l) return fail("reader: %s: the size line needs rows, columns and entries", path.c_str());
-                    cap = symmetric ? 2 * c : c;
-                }
-                if (a < 0 || b < 0 || cap < 0) return fail("reader: %s: negative size", path.c_str());
-                m->nrows = a;
-                m->ncols = b;
-                m->row.reserve((size_t)cap);
-                m->col.reserve((size_t)cap);
-                m->val.reserve((size_t)cap);
-                have_size = true;
+            long long a = strtoll(l, &t, 10);
+            if (t == l) return fail("reader: %s: bad size line", path.c_str());
+            l = t;
+            long long b = strtoll(l, &t, 10);
+            if (t == l) return fail("reader: %s: bad size line", path.c_str());
+            l = t;
+            long long c = strtoll(l, &t, 10);
+            if (h->array) {
+                h->capacity = a * b;
             } else {
-                if ((int64_t)m->row.size() >= cap) return fail("reader: %s: more entries than the size line announces", path.c_str());
-                int64_t r, c;
-                double v;
-                if (array) {
-                    v = strtod(l, nullptr);
-                    c = m->nrows ? seen / m->nrows : 0;
-                    r = seen - m->nrows * c;
-                } else {
-                    r = strtoll(l, &t, 0);
-                    if (t == l) return fail("reader: %s: bad entry line", path.c_str());
-                    l = t;
-                    c = strtoll(l, &t, 0);
-                    if (t == l) return fail("reader: %s: bad entry line", path.c_str());
-                    l = t;
-                    v = strtod(l, &t);
-                    if (t == l) v = 1.0;                // pattern file
-                    r -= 1;
-                    c -= 1;
-                }
-                if (r < 0 || r >= m->nrows || c < 0 || c >= m->ncols)
-                    return fail("reader: %s: entry (%lld, %lld) outside %lld x %lld", path.c_str(), (long long)r + 1,
-                                (long long)c + 1, (long long)m->nrows, (long long)m->ncols);
-                m->row.push_back(r); m->col.push_back(c); m->val.push_back(v);
-                seen++;
-                if (symmetric && r != c) {
-                    m->row.push_back(c); m->col.push_back(r); m->val.push_back(skew ? -v : v);
-                }
+                if (t == l) return fail("reader: %s: the size line needs rows, columns and entries", path.c_str());
+                h->capacity = h->symmetric ? 2 * c : c;
             }
+            if (a < 0 || b < 0 || h->capacity < 0) return fail("reader: %s: negative size", path.c_str());
+            h->nrows = a;
+            h->ncols = b;
+            h->body = (size_t)(next - text.data());
+            return 0;
         }
-        p = nl ? nl + 1 : end;
+        p = next;
     }
-    if (!have_size) return fail("reader: %s: no size line", path.c_str());
-    return 0;
+    return fail("reader: %s: no size line", path.c_str());
 }
 
-// parse + device sort, once per path
+// read the file, parse its entry lines and sort the entries on the device, once per path
 static SortedFile *open_sorted(int32_t file_id)
 {
     char name[64];
@@ -137,10 +108,22 @@ static SortedFile *open_sorted(int32_t file_id)
     std::lock_guard<std::mutex> lk(g_files_mu);
     auto it = g_files.find(path);
     if (it != g_files.end()) return it->second;
+
+    FILE *f = fopen(path, "rb");
+    if (!f) { fail("reader: cannot open %s", path); return nullptr; }
+    std::string text;
+    {
+        char buf[1 << 16];
+        size_t got;
+        while ((got = fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, got);
+        fclose(f);
+    }
+    MarketHeader h;
+    if (parse_header(path, text, &h)) return nullptr;
     SortedFile *m = new SortedFile();
-    if (parse_market(path, m)) { delete m; return nullptr; }
-    const int64_t n = (int64_t)m->row.size();
-    if (n > 0) {
+    m->nrows = h.nrows;
+    m->ncols = h.ncols;
+    if (text.size() > h.body) {
         int ndev = 0;
         if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
             fail("no CUDA device is available; libcomet_b200 has no CPU path");
@@ -148,26 +131,23 @@ static SortedFile *open_sorted(int32_t file_id)
             return nullptr;
         }
         cudaStream_t st = lib_stream();
-        int64_t *dr = nullptr, *dc = nullptr;
+        int64_t *dr = nullptr, *dc = nullptr, n = 0;
         double *dv = nullptr, *dv2 = nullptr;
-        bool ok = cudaMallocAsync((void **)&dr, (size_t)n * 8, st) == cudaSuccess &&
-                  cudaMallocAsync((void **)&dc, (size_t)n * 8, st) == cudaSuccess &&
-                  cudaMallocAsync((void **)&dv, (size_t)n * 8, st) == cudaSuccess &&
-                  cudaMallocAsync((void **)&dv2, (size_t)n * 8, st) == cudaSuccess;
-        if (ok) {
-            cudaMemcpyAsync(dr, m->row.data(), (size_t)n * 8, cudaMemcpyHostToDevice, st);
-            cudaMemcpyAsync(dc, m->col.data(), (size_t)n * 8, cudaMemcpyHostToDevice, st);
-            cudaMemcpyAsync(dv, m->val.data(), (size_t)n * 8, cudaMemcpyHostToDevice, st);
-            // the coordinates may be sorted in place (they are rebuilt from the keys); the values are gathered
-            ok = sort_coo(n, m->nrows, m->ncols, dr, dc, dv, dr, dc, dv2, st) == 0;
-        } else {
-            fail("reader: device allocation failed");
-        }
-        if (ok) {
-            cudaMemcpyAsync(m->row.data(), dr, (size_t)n * 8, cudaMemcpyDeviceToHost, st);
-            cudaMemcpyAsync(m->col.data(), dc, (size_t)n * 8, cudaMemcpyDeviceToHost, st);
-            cudaMemcpyAsync(m->val.data(), dv2, (size_t)n * 8, cudaMemcpyDeviceToHost, st);
-            if (cudaStreamSynchronize(st) != cudaSuccess) { fail("reader: copy of the sorted entries failed"); ok = false; }
+        bool ok = parse_market_body_on_device(path, text.data() + h.body, (int64_t)(text.size() - h.body), h.array,
+                                              h.symmetric, h.skew, h.nrows, h.ncols, h.capacity, &dr, &dc, &dv, &n,
+                                              st) == 0;
+        if (ok && n > 0) {
+            ok = cudaMallocAsync((void **)&dv2, (size_t)n * 8, st) == cudaSuccess;
+            if (!ok) fail("reader: device allocation failed");
+            // the coordinates are sorted in place (they are rebuilt from the keys); the values are gathered
+            if (ok) ok = sort_coo(n, m->nrows, m->ncols, dr, dc, dv, dr, dc, dv2, st) == 0;
+            if (ok) {
+                m->row.resize((size_t)n); m->col.resize((size_t)n); m->val.resize((size_t)n);
+                cudaMemcpyAsync(m->row.data(), dr, (size_t)n * 8, cudaMemcpyDeviceToHost, st);
+                cudaMemcpyAsync(m->col.data(), dc, (size_t)n * 8, cudaMemcpyDeviceToHost, st);
+                cudaMemcpyAsync(m->val.data(), dv2, (size_t)n * 8, cudaMemcpyDeviceToHost, st);
+                if (cudaStreamSynchronize(st) != cudaSuccess) { fail("reader: copy of the sorted entries failed"); ok = false; }
+            }
         }
         if (dr) cudaFreeAsync(dr, st);
         if (dc) cudaFreeAsync(dc, st);

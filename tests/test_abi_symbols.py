@@ -53,9 +53,14 @@ def test_reader_needs_a_device_and_reports_bad_files(tmp_path):
     with pytest.raises(CometB200Error, match="cannot open"):
         api.read_mtx(str(tmp_path / "missing.mtx"))
     bad = tmp_path / "bad.mtx"
-    bad.write_text("%%MatrixMarket matrix coordinate real general\n2 2 1\n3 1 1.0\n")
-    with pytest.raises(CometB200Error, match="outside"):
+    bad.write_text("%%MatrixMarket matrix coordinate real general\n2 2\n3 1 1.0\n")
+    with pytest.raises(CometB200Error, match="size line needs"):       # the header is parsed on the host
         api.read_mtx(str(bad))
+    if torch.cuda.is_available():                                      # the entry lines are parsed on the device
+        bad.write_text("%%MatrixMarket matrix coordinate real general\n2 2 1\n3 1 1.0\n")
+        os.environ.pop("SPARSE_FILE_NAME0", None)
+        with pytest.raises(CometB200Error, match="outside"):
+            api.read_mtx(str(bad), file_id=1)
     if not torch.cuda.is_available():
         ok = tmp_path / "ok.mtx"
         ok.write_text("%%MatrixMarket matrix coordinate real general\n2 2 1\n2 1 1.0\n")
