@@ -328,6 +328,36 @@ class SpMV(Workload):
     def step(self, dev):
         dev.spmv(self.dA, self.dx, self.dy)
 
+    def latency_table(self, dev):
+        """Per-call time of back-to-back SpMVs replayed from a CUDA graph of 1, 10 and 1000 calls, and of the
+        same graphs filled with EMPTY kernels: the floor set by launching, not by the kernel."""
+        torch = self.torch
+        lib = self.lib()
+        out = {}
+
+        def timed(fill, n):
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(n):
+                    fill()
+            for _ in range(3):
+                g.replay()
+            reps = max(3, 2000 // n)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / (reps * n)
+
+        noop = lambda: lib.comet_b200_dev_noop(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        for n in (1, 10, 1000):
+            out["calls_%d" % n] = {"spmv_us_per_call": timed(lambda: dev.spmv(self.dA, self.dx, self.dy), n),
+                                   "empty_kernel_us_per_call": timed(noop, n)}
+        return out
+
     def finish_step(self, sharding):
         if self.world > 1:
             self.y_full = sharding.all_gather_rows(self.dy, self.bounds)
@@ -912,6 +942,8 @@ def measure(w, args, env, headline):
         res["probes_per_s"] = w.probes / (ms_per_step * 1e-3)
     if hasattr(w, "total_nnz_c"):
         res["nnz_c"] = w.total_nnz_c
+    if hasattr(w, "latency_table") and world == 1 and not args.kernel_only:
+        res["latency"] = w.latency_table(dev)
     if rank == 0 and world == 1 and not args.no_cpu and not args.kernel_only:
         res["cpu_baseline"] = cpu_baseline(w)
     return res, parity_ok
@@ -1042,7 +1074,7 @@ def main():
         }
         for key in ("e2e", "e2e_pageable", "gpu_launches", "roofline", "per_rank_kernel_ms", "parity_checked",
                     "cpu_baseline", "rebalance_per_rank_ms", "row_bounds", "e2e_row_bounds", "e2e_row_bounds_note",
-                    "probes_per_s", "nnz_c"):
+                    "probes_per_s", "nnz_c", "latency"):
             if key in head:
                 line[key] = head[key]
         if others:

@@ -82,6 +82,7 @@ SIGNATURES = {
                                                                 [POINTER(c_int64), POINTER(c_int64), c_void_p]),
     "comet_b200_dev_spgemm_numeric_f64_i64": (c_int32, [c_int64, c_void_p, c_void_p, c_int32, c_void_p]),
     "comet_b200_dev_masked_spgemm_count_f64_i64": (c_int32, [c_int64] * 6 + [c_void_p] * 7 + [c_void_p]),
+    "comet_b200_dev_noop": (c_int32, [c_void_p]),
     "comet_b200_dev_gather_probe_f64_i64": (c_int32, [c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32,
                                                       c_void_p, c_int64, c_void_p]),
 }

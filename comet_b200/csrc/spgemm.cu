@@ -53,6 +53,7 @@ struct Plan {
     unsigned n1, n2;
     uint32_t *bm_store;      // n2 * words, or null
     int words;
+    cudaStream_t last;       // stream of the latest call on this plan: its arrays are released in that stream's order
 };
 
 static std::mutex g_plans_mu;
@@ -730,6 +731,7 @@ int spgemm_symbolic(int64_t nrows, int64_t ncols_b, int64_t nnz_b, const int64_t
     Plan *p = new Plan();
     memset(p, 0, sizeof(Plan));
     p->kind = 0; p->nrows = nrows; p->ncols = ncols_b; p->nnz_b = nnz_b;
+    p->last = st;
     p->apos = apos; p->acrd = acrd; p->aval = aval; p->bpos = bpos; p->bcrd = bcrd; p->bval = bval;
     p->mpos = mpos; p->mcrd = mpos ? mcrd : nullptr; p->semi = semiring;
     p->cpos = cpos;
@@ -807,6 +809,7 @@ int elews_ss_symbolic(int64_t nrows, const int64_t *apos, const int64_t *acrd, c
     Plan *p = new Plan();
     memset(p, 0, sizeof(Plan));
     p->kind = 1; p->nrows = nrows;
+    p->last = st;
     p->apos = apos; p->acrd = acrd; p->aval = aval; p->bpos = bpos; p->bcrd = bcrd; p->bval = bval;
     p->cpos = cpos;
     int rc = dev_alloc(&p->cnt, (size_t)nrows + 1, st);
@@ -829,6 +832,7 @@ int sparse_out_numeric(int64_t handle, int64_t *ccrd, double *cval, int keep, cu
 {
     Plan *p = find_plan(handle, !keep);
     if (!p) return fail("numeric phase: unknown handle %lld", (long long)handle);
+    p->last = st;
     int rc = 0;
     if (p->kind == 1) {
         if (p->nrows > 0) {
@@ -903,8 +907,9 @@ int sparse_out_numeric(int64_t handle, int64_t *ccrd, double *cval, int keep, cu
 
 void destroy_plan(int64_t handle)
 {
+    // a numeric launch of a kept plan may still be running: free behind it, in its own stream's order
     Plan *p = find_plan(handle, true);
-    if (p) plan_free(p, nullptr);
+    if (p) plan_free(p, p->last);
 }
 
 }  // namespace cb200

@@ -74,6 +74,12 @@ spmv_kernel(int64_t nrows, const int64_t *__restrict__ row_ids, const int64_t *_
     const int lane = threadIdx.x & 31;
     const unsigned gmask = (T == 32) ? 0xffffffffu : (((1u << T) - 1u) << (lane & ~(T - 1)));
     if (threadIdx.x == 0) n_long = 0;
+    // Programmatic dependent launch: when the launch carries that attribute this grid may be set up while the
+    // kernel before it in the stream is still running; nothing that kernel may have written (x, y, even A) is
+    // touched before the wait, and the next kernel in the stream is allowed to set up from here on.  Without
+    // the attribute both instructions do nothing.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __syncthreads();
 
     const int64_t row0 = (int64_t)blockIdx.x * (GROUPS * passes);
@@ -174,7 +180,22 @@ static int launch_spmv(int64_t nrows, const int64_t *row_ids, const int64_t *pos
     int passes = SPMV_PASSES;
     while (passes > 1 && ceil_div(nrows, (int64_t)GROUPS * passes) < (int64_t)sm_count() * 4) passes--;
     unsigned grid = (unsigned)ceil_div(nrows, (int64_t)GROUPS * passes);
-#define GO(P, V) spmv_kernel<T, P, V><<<grid, SPMV_THREADS, 0, st>>>(nrows, row_ids, pos, crd, val, x, y, accumulate, passes, hdr, chunks, (unsigned)cap)
+    // One-launch calls (no chunk list) are a few microseconds long, so back-to-back calls are bound by the gap
+    // between launches: they are launched with programmatic stream serialization, which lets the next grid be
+    // set up under the tail of this one (COMET_B200_SPMV_PDL=0 switches it off).
+    static const bool pdl = [] { const char *e = getenv("COMET_B200_SPMV_PDL"); return !(e && e[0] == '0'); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(SPMV_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl && !hdr) ? 1 : 0;
+    const unsigned ucap = (unsigned)cap;
+#define GO(P, V) CB_CUDA(cudaLaunchKernelEx(&cfg, spmv_kernel<T, P, V>, nrows, row_ids, pos, crd, val, x, y, accumulate, passes, hdr, chunks, ucap))
     if (pair) { if (vec) GO(true, true); else GO(true, false); }
     else      { if (vec) GO(false, true); else GO(false, false); }
 #undef GO

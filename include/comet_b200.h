@@ -618,6 +618,9 @@ COMET_B200_EXPORT int32_t comet_b200_dev_gather_probe_f64_i64(int64_t nnz, const
                                                               int32_t ctas_per_sm, double *out, int64_t out_len,
                                                               void *stream);
 
+/* Measurement aid: launches an empty kernel on `stream` (the launch floor of back-to-back small calls). */
+COMET_B200_EXPORT int32_t comet_b200_dev_noop(void *stream);
+
 /* Frees the library's scratch memory on the current device. */
 COMET_B200_EXPORT void comet_b200_release_scratch(void);
 
