@@ -212,6 +212,9 @@ spmm_scalar_kernel(int64_t nrows, const int64_t *__restrict__ row_ids,
 int spmm_stream(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_t *row_ids, const int64_t *pos,
                 const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
                 int accumulate, bool forced, cudaStream_t st);
+int spmm_stream_tma(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_t *row_ids, const int64_t *pos,
+                    const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
+                    int accumulate, cudaStream_t st);
 
 // Shapes the entry-stream path takes without being asked.
 // From 64 columns on a row of B fills the lanes of a warp and the stream wins on uniform and
@@ -300,8 +303,14 @@ int spmm_rows(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_
         CB_LAUNCH_CHECK();
         return 0;
     }
-    // bits 24-25 of the variant pick the path: 0 = by shape, 1 = entry stream (rows of B staged in shared memory by cp.async), 2 = row panels
+    // bits 24-25 of the variant pick the path: 0 = by shape, 1 = entry stream (rows of B staged in shared memory by
+    // cp.async), 2 = row panels, 3 = entry stream with the rows staged by TMA bulk copies
     const int path = (variant >> 24) & 3;
+    if (!pair && path == 3) {
+        const int took = spmm_stream_tma(nrows, ncols, nnz, k, row_ids, pos, crd, val, b, ldb, c, ldc, accumulate, st);
+        if (took < 0) return -1;
+        if (took > 0) return 0;
+    }
     if (!pair && path != 2 && (path == 1 || spmm_stream_preferred(nrows, nnz, k))) {
         const int took = spmm_stream(nrows, ncols, nnz, k, row_ids, pos, crd, val, b, ldb, c, ldc, accumulate, path == 1, st);
         if (took < 0) return -1;

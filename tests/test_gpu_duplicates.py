@@ -93,7 +93,7 @@ def test_spmv_chunk_list_path_with_repeated_coordinates():
     _close(api.spmv(A, x), oracle.spmv(_orc(A), x), oracle.spmv(_abs(A), np.abs(x)))
 
 
-@pytest.mark.parametrize("variant", [1 << 24, 2 << 24])     # entry stream, row panels
+@pytest.mark.parametrize("variant", [1 << 24, 2 << 24, 3 << 24])     # entry stream, row panels, TMA-staged stream
 @pytest.mark.parametrize("k", [128, 16])
 def test_spmm_with_repeated_coordinates(variant, k):
     n = 3000

@@ -109,19 +109,28 @@ def _gappy(n=6000, seed=5):
 
 @pytest.mark.parametrize("k", [128, 64, 96, 16, 2, 256])
 @pytest.mark.parametrize("make", [_gappy, _skewed])
-def test_spmm_entry_stream_path(make, k):
-    """The entry-stream kernel (asked for by bit 24 of the variant; the default from 64 columns and
-    65536 entries on): rows cut by block boundaries, empty rows at every position, both store modes."""
+@pytest.mark.parametrize("family", [1, 3])
+def test_spmm_entry_stream_path(make, k, family):
+    """The entry-stream kernels (asked for by bits 24-25 of the variant: 1 = rows of B staged with cp.async,
+    the default from 64 columns on; 3 = staged by TMA bulk copies completing on mbarriers): rows cut by
+    block boundaries, empty rows at every position, both store modes."""
     A = make()
     B = datasets.dense_uniform((A.ncols, k), 3)
     C0 = datasets.dense_uniform((A.nrows, k), 4)
     scale = oracle.spmm(_abs(A), np.abs(B), np.abs(C0))
     dA = dev.to_device(A)
     dB = torch.from_numpy(B).cuda()
-    C = dev.spmm(dA, dB, variant=1 << 24)
+    C = dev.spmm(dA, dB, variant=family << 24)
     _close(C.cpu().numpy(), oracle.spmm(_orc(A), B), scale)
-    C = dev.spmm(dA, dB, torch.from_numpy(C0).cuda(), accumulate=True, variant=1 << 24)
+    C = dev.spmm(dA, dB, torch.from_numpy(C0).cuda(), accumulate=True, variant=family << 24)
     _close(C.cpu().numpy(), oracle.spmm(_orc(A), B, C0), scale)
+
+
+def test_spmm_tma_staging_on_a_power_law_matrix():
+    A, B = datasets.config_spmm(scale=14, edge_factor=16, k=128)
+    dA, dB = dev.to_device(A), torch.from_numpy(B).cuda()
+    C = dev.spmm(dA, dB, variant=3 << 24)
+    _close(C.cpu().numpy(), oracle.spmm(_orc(A), B), oracle.spmm(_abs(A), np.abs(B)))
 
 
 def test_spmm_entry_stream_path_dcsr(tmp_path):
