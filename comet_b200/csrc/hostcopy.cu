@@ -33,7 +33,7 @@ namespace {
 
 const size_t CHUNK = (size_t)4 << 20;     // bytes per page-locked chunk
 const int SLOTS = 12;                     // chunks per device (48 MiB of page-locked memory)
-const size_t STAGE_MIN_DEFAULT = (size_t)1 << 20;   // smaller copies are left to the driver
+const size_t STAGE_MIN_DEFAULT = (size_t)16 << 20;  // smaller copies are left to the driver (waking the workers costs more)
 
 struct Slot {
     char *buf = nullptr;

@@ -37,6 +37,7 @@ def _spmm_window(A, wide_b, col0, k, out, out0):
 @pytest.mark.parametrize("mode", ["staged", "driver", "page-locked"])
 @pytest.mark.parametrize("panels", [True, False])
 def test_spmm_through_pageable_host_arrays(monkeypatch, mode, panels):
+    monkeypatch.setenv("COMET_B200_STAGE_MIN_BYTES", str(1 << 20))
     A = datasets.rmat_csr(15, 8, seed=2)                       # 32768 rows: B and C are 33.5 MB each at K = 128
     k = 128
     wide = datasets.dense_uniform((A.ncols, k + 10), 3)        # B is a column window: rows 1104 bytes apart
