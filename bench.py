@@ -44,6 +44,39 @@ NOMINAL_HBM_GBS = 8000.0
 RTOL = 1e-12
 
 
+# DRAM traffic of one step (dram__bytes_read.sum + dram__bytes_write.sum over the step's kernels, one-pass ncu
+# capture at the full workload on one GPU) is kept in profiles/dram_traffic.json together with a hash of the
+# kernel sources it was taken from; it is reported only while those sources are unchanged.
+KERNEL_SOURCES = {
+    "spmm": ["spmm_stream.cu", "stream.cuh", "spmm.cu"],
+    "sddmm": ["sddmm.cu"],
+    "spgemm": ["spgemm.cu", "util.cu"],
+    "triangles": ["tc.cu"],
+}
+
+
+def kernel_source_hash(name):
+    import hashlib
+    h = hashlib.sha256()
+    for f in KERNEL_SOURCES.get(name, []):
+        with open(os.path.join(ROOT, "comet_b200", "csrc", f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def recorded_traffic(name, default_size):
+    if not default_size or name not in KERNEL_SOURCES:
+        return None
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            rec = json.load(f).get(name)
+        if rec and rec.get("kernel_source_hash") == kernel_source_hash(name):
+            return float(rec["dram_bytes_per_step"])
+    except Exception:
+        pass
+    return None
+
+
 def measured_peak():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -929,7 +962,10 @@ def measure(w, args, env, headline):
         "parity_checked": parity_ok,
         "gpu_launches": w.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "traffic": None, "peak_kind": peak_kind,
+                     "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS,
+                     "traffic": recorded_traffic(w.name, world == 1 and not args.scale and not args.k and not args.variant),
+                     "traffic_source": "profiles/dram_traffic.json (ncu, one GPU, same kernel sources) or null",
+                     "peak_kind": peak_kind,
                      "algorithmic_bytes_per_step": int(rank_bytes), "kernel_ms_per_step": slowest,
                      "gather_model_gbs": (w.gather_model_bytes / world) / (slowest * 1e-3) / 1e9,
                      "gather_model_note": "no-reuse model: one dense row fetched per stored entry / product / probe"},
