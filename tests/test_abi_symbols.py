@@ -112,3 +112,15 @@ def test_default_error_mode_exits_like_the_reference_runtime():
     assert r.returncode == 1
     assert "libcomet_b200: ERROR" in r.stderr and "unknown handle" in r.stderr
     assert "survived" not in r.stdout
+
+
+def test_the_concurrency_contract_of_the_device_layer_is_stated_where_callers_look():
+    """The device-pointer entry points keep their work lists and counters in one scratch area per device, so
+    calls on one device must not overlap.  That is a contract, not something the library can enforce across
+    streams; it has to be written where a caller reads: beside the layer-2 declarations and in the
+    integration notes."""
+    header = open(os.path.join(ROOT, "include", "comet_b200.h")).read()
+    layer2 = header[header.index("Layer 2: device pointers"):]
+    assert "must therefore not overlap" in layer2 and "one stream at a time" in layer2
+    notes = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    assert "One call at a time per device" in notes
