@@ -338,9 +338,17 @@ class SpMV(Workload):
     def to_device(self, block, torch, dev):
         self.dA = dev.to_device(block)
         self.dx = torch.from_numpy(self.x).cuda()
-        self.dy = torch.empty(block.nrows, dtype=torch.float64, device="cuda")
         self.torch = torch
         self.graphs = {}
+        if self.world == 1:
+            self.dy = torch.empty(block.nrows, dtype=torch.float64, device="cuda")
+        else:
+            # y blocks are exchanged in place: one buffer of `world` equal slices (the longest block, rounded up to
+            # 256 bytes), every rank's kernel writes its slice, the library's all-gather fills in the others
+            longest = max(int(self.bounds[r + 1] - self.bounds[r]) for r in range(self.world))
+            self.slice_elems = (longest * 8 + 255) // 256 * 32
+            self.ybuf = torch.zeros(self.world * self.slice_elems, dtype=torch.float64, device="cuda")
+            self.dy = self.ybuf[self.rank * self.slice_elems:self.rank * self.slice_elems + block.nrows]
 
     def run_steps(self, n, dev, sharding, with_collective=True):
         # One SpMV at this size is shorter than a kernel launch from the host, so on one GPU
@@ -393,15 +401,21 @@ class SpMV(Workload):
 
     def finish_step(self, sharding):
         if self.world > 1:
-            self.y_full = sharding.all_gather_rows(self.dy, self.bounds)
+            from comet_b200 import _lib
+            st = ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+            _lib.check(self.lib().comet_b200_dev_allgather_slices(ctypes.c_void_p(self.ybuf.data_ptr()),
+                                                                  self.slice_elems * 8, st))
 
     def check(self, torch, dev):
         from oracle import oracle
         ref = oracle.spmv(_orc(self.block), self.x)
         ok = _within(self.dy.cpu().numpy(), ref, oracle.spmv(_orc_abs(self.block), np.abs(self.x)))
-        if self.world > 1:
+        if self.world > 1:      # the gathered vector: every rank's slice, cut to its block length
+            buf = self.ybuf.cpu().numpy()
+            parts = [buf[r * self.slice_elems:r * self.slice_elems + int(self.bounds[r + 1] - self.bounds[r])]
+                     for r in range(self.world)]
             full = oracle.spmv(_orc(self.A), self.x)
-            ok = ok and _within(self.y_full.cpu().numpy(), full, oracle.spmv(_orc_abs(self.A), np.abs(self.x)))
+            ok = ok and _within(np.concatenate(parts), full, oracle.spmv(_orc_abs(self.A), np.abs(self.x)))
         return ok
 
     def e2e_setup(self, torch, pinned):

@@ -766,7 +766,11 @@ int spgemm_symbolic(int64_t nrows, int64_t ncols_b, int64_t nnz_b, const int64_t
     }
     if (!rc && p->n2) {
         size_t store = (size_t)p->n2 * p->words * sizeof(uint32_t);
-        if (store <= BM_STORE_BUDGET) {
+        // the symbolic pass's bitmaps are kept for the numeric pass while they fit the budget
+        // (COMET_B200_SPGEMM_BITMAP_GB overrides it; 0 makes the numeric pass mark its rows again)
+        size_t budget = BM_STORE_BUDGET;
+        if (const char *e = getenv("COMET_B200_SPGEMM_BITMAP_GB")) budget = (size_t)(atof(e) * (double)(1ull << 30));
+        if (store <= budget) {
             cudaError_t e = cudaMallocAsync((void **)&p->bm_store, store, st);
             if (e != cudaSuccess) { p->bm_store = nullptr; (void)cudaGetLastError(); }
         }
