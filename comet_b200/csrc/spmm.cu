@@ -214,7 +214,7 @@ int spmm_stream(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int6
                 int accumulate, bool forced, cudaStream_t st);
 int spmm_stream_tma(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_t *row_ids, const int64_t *pos,
                     const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
-                    int accumulate, cudaStream_t st);
+                    int accumulate, bool gather4, cudaStream_t st);
 
 // Shapes the entry-stream path takes without being asked.
 // From 64 columns on a row of B fills the lanes of a warp and the stream wins on uniform and
@@ -304,10 +304,12 @@ int spmm_rows(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_
         return 0;
     }
     // bits 24-25 of the variant pick the path: 0 = by shape, 1 = entry stream (rows of B staged in shared memory by
-    // cp.async), 2 = row panels, 3 = entry stream with the rows staged by TMA bulk copies
+    // cp.async), 2 = row panels, 3 = entry stream with the rows staged by TMA bulk copies (bit 26 in addition: one
+    // tile::gather4 tensor copy per stage instead of one bulk copy per row)
     const int path = (variant >> 24) & 3;
     if (!pair && path == 3) {
-        const int took = spmm_stream_tma(nrows, ncols, nnz, k, row_ids, pos, crd, val, b, ldb, c, ldc, accumulate, st);
+        const int took = spmm_stream_tma(nrows, ncols, nnz, k, row_ids, pos, crd, val, b, ldb, c, ldc, accumulate,
+                                         ((variant >> 26) & 1) != 0, st);
         if (took < 0) return -1;
         if (took > 0) return 0;
     }

@@ -13,8 +13,16 @@
 // already in flight the same bounded time to land, and leaves (the result is then incomplete; a correct run
 // cannot get there, since a stage's expected byte count equals the bytes of the copies issued for it).
 //
-// Selected with bits 24-25 of the SpMM variant = 3; the cp.async kernel stays the default (see the profiles
-// for the measured difference).
+// A second form fills a stage with ONE instruction: the sm_100 tensor copy with four row coordinates,
+// `cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4`, over a 2-D tensor map of this GPU's own B
+// (box = one row of K doubles; the four rows named by the instruction land one after the other in shared
+// memory, which is exactly a stage).  No cluster multicast anywhere.
+//
+// Selected with bits 24-25 of the SpMM variant = 3 (row-wise bulk copies) and bit 26 in addition (gather4);
+// see the profiles for the measured differences to the cp.async kernel.
+#include <cuda.h>
+#include <string.h>
+
 #include "common.cuh"
 #include "stream.cuh"
 
@@ -23,7 +31,8 @@ namespace cb200 {
 static const int ST_WARPS = 16;
 static const int ST_G = 4;                      // rows of B per stage
 static const int ST_RING_BYTES = 12 * 1024;     // per warp
-static const int ST_SIDE_BYTES = 512 + 64;      // 32 column indices, 32 values, 32 row ends, up to 8 barriers
+static const int ST_SIDE_BYTES = 512 + 128;     // 32 column indices, 32 values, 32 row ends, up to 8 barriers; keeps every
+                                                // warp's ring 128-byte aligned, which the tensor copy asks of its destination
 static const unsigned ST_WAIT_LIMIT = 1u << 24; // polls of one barrier before giving up
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, unsigned count)
@@ -47,9 +56,19 @@ __device__ __forceinline__ void bulk_row(uint32_t dst, const void *src, unsigned
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-template <int NI>
+// four rows of the tensor behind `tmap`, columns from c0 on, rows r0..r3, into 4 consecutive rows at dst
+__device__ __forceinline__ void gather4_rows(uint32_t dst, const CUtensorMap *tmap, int c0, int r0, int r1, int r2, int r3,
+                                             uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                 ::"r"(dst), "l"(tmap), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
+}
+
+template <int NI, bool G4>
 __global__ void __launch_bounds__(ST_WARPS * 32, 1)
-spmm_stream_tma_kernel(int64_t nrows, int64_t nnz, unsigned nblocks, const int64_t *__restrict__ row_ids,
+spmm_stream_tma_kernel(const __grid_constant__ CUtensorMap tmap, int64_t nrows, int64_t nnz, unsigned nblocks,
+                       const int64_t *__restrict__ row_ids,
                        const int64_t *__restrict__ pos, const int64_t *__restrict__ crd, const double *__restrict__ val,
                        const double *__restrict__ b, int64_t ldb, double *__restrict__ c, int64_t ldc, int k, int stages,
                        int accumulate, WorkHeader *hdr, const int64_t *__restrict__ block_row,
@@ -175,12 +194,24 @@ spmm_stream_tma_kernel(int64_t nrows, int64_t nnz, unsigned nblocks, const int64
             const int m = (cnt - g * ST_G) < ST_G ? (cnt - g * ST_G) : ST_G;
             const unsigned s = fill % (unsigned)stages;
             const uint32_t bar = bars + 8u * s;
-            if (lane == 0) mbar_expect(bar, (unsigned)m * rowbytes);
-            __syncwarp();
-            if (lane < m) {
-                const int col = cs[off + lane];
-                bulk_row(ring_s + s * stagebytes + (uint32_t)lane * rowbytes, (const char *)b + (int64_t)col * ldb * 8,
-                         rowbytes, bar);
+            if (G4) {
+                // one instruction for the stage; a stage at the end of a piece with fewer than four entries names
+                // its last row again (the copies beyond m are not read)
+                __syncwarp();                            // every lane is done reading the stage this one replaces
+                if (lane == 0) {
+                    const int4 c4 = *(const int4 *)(cs + off);
+                    const int r0 = c4.x, r1 = m > 1 ? c4.y : r0, r2 = m > 2 ? c4.z : r1, r3 = m > 3 ? c4.w : r2;
+                    mbar_expect(bar, stagebytes);
+                    gather4_rows(ring_s + s * stagebytes, &tmap, 0, r0, r1, r2, r3, bar);
+                }
+            } else {
+                if (lane == 0) mbar_expect(bar, (unsigned)m * rowbytes);
+                __syncwarp();
+                if (lane < m) {
+                    const int col = cs[off + lane];
+                    bulk_row(ring_s + s * stagebytes + (uint32_t)lane * rowbytes, (const char *)b + (int64_t)col * ldb * 8,
+                             rowbytes, bar);
+                }
             }
             fill++;
         };
@@ -252,10 +283,37 @@ spmm_stream_tma_kernel(int64_t nrows, int64_t nnz, unsigned nblocks, const int64
     }
 }
 
+// 2-D tensor map of B for the gather4 form: dimension 0 = the K columns of a row, dimension 1 = the rows,
+// box = one row.  cuTensorMapEncodeTiled is looked up through the runtime, so the library does not link libcuda.
+static int make_row_map(const double *b, int64_t nrows_b, int64_t k, int64_t ldb, CUtensorMap *map)
+{
+    typedef CUresult (*Encode)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Encode encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
+            q != cudaDriverEntryPointSuccess)
+            return fail("spmm: cuTensorMapEncodeTiled is not available from this driver");
+        encode = (Encode)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)nrows_b};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldb * 8};
+    const cuuint32_t box[2] = {(cuuint32_t)k, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 2, (void *)b, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("spmm: cuTensorMapEncodeTiled refused the map of B (error %d)", (int)r);
+    return 0;
+}
+
 // Returns 1 when this path took the call, 0 when the shape is not one it handles, -1 on error.
 int spmm_stream_tma(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const int64_t *row_ids, const int64_t *pos,
                     const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
-                    int accumulate, cudaStream_t st)
+                    int accumulate, bool gather4, cudaStream_t st)
 {
     // bulk copies need 16-byte aligned rows whose size is a multiple of 16 bytes
     if (k < 2 || k > 256 || (k & 1) || (ldb & 1) || (ldc & 1) || ((((uintptr_t)b | (uintptr_t)c) & 15) != 0)) return 0;
@@ -265,6 +323,13 @@ int spmm_stream_tma(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const 
     if (stages > 8) stages = 8;
     if (stages < 2) return 0;
     const size_t smem = (size_t)ST_WARPS * ((size_t)stages * ST_G * rowbytes + ST_SIDE_BYTES);
+    alignas(64) CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    if (gather4) {
+        // every stage must start on a 128-byte boundary of shared memory: rows of at least 32 bytes
+        if ((ST_G * rowbytes) % 128 != 0 || ldb * 8 >= (1LL << 40)) return 0;
+        if (make_row_map(b, ncols, k, ldb, &map)) return -1;
+    }
 
     StreamPlan plan;
     const int planned = stream_plan(nrows, nnz, (int64_t)sm_count() * ST_WARPS, row_ids, pos, c, ldc, (int)k, accumulate,
@@ -273,20 +338,26 @@ int spmm_stream_tma(int64_t nrows, int64_t ncols, int64_t nnz, int64_t k, const 
     int64_t grid = ceil_div(plan.nblocks, ST_WARPS);
     if (grid > sm_count()) grid = sm_count();
     const int ni = k <= 64 ? 1 : (k <= 128 ? 2 : 4);
-#define ST_LAUNCH(NN)                                                                                                  \
+#define ST_LAUNCH(NN, GG)                                                                                              \
     do {                                                                                                               \
-        if (cudaFuncSetAttribute(spmm_stream_tma_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+        if (cudaFuncSetAttribute(spmm_stream_tma_kernel<NN, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
                                  ST_WARPS * (ST_RING_BYTES + ST_SIDE_BYTES)) != cudaSuccess) {                         \
             fail("spmm: shared memory size refused");                                                                  \
             return -1;                                                                                                 \
         }                                                                                                              \
-        spmm_stream_tma_kernel<NN><<<(unsigned)grid, ST_WARPS * 32, smem, st>>>(                                       \
-            nrows, nnz, (unsigned)plan.nblocks, row_ids, pos, crd, val, b, ldb, c, ldc, (int)k, stages, accumulate,    \
-            plan.hdr, plan.block_row, plan.block_ent);                                                                 \
+        spmm_stream_tma_kernel<NN, GG><<<(unsigned)grid, ST_WARPS * 32, smem, st>>>(                                   \
+            map, nrows, nnz, (unsigned)plan.nblocks, row_ids, pos, crd, val, b, ldb, c, ldc, (int)k, stages,           \
+            accumulate, plan.hdr, plan.block_row, plan.block_ent);                                                     \
     } while (0)
-    if (ni == 1) ST_LAUNCH(1);
-    else if (ni == 2) ST_LAUNCH(2);
-    else ST_LAUNCH(4);
+    if (gather4) {
+        if (ni == 1) ST_LAUNCH(1, true);
+        else if (ni == 2) ST_LAUNCH(2, true);
+        else ST_LAUNCH(4, true);
+    } else {
+        if (ni == 1) ST_LAUNCH(1, false);
+        else if (ni == 2) ST_LAUNCH(2, false);
+        else ST_LAUNCH(4, false);
+    }
 #undef ST_LAUNCH
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

@@ -70,7 +70,10 @@ def spmv(A, x, y=None, semiring=PLUS_TIMES, accumulate=False):
 
 
 def spmm(A, B, C=None, semiring=PLUS_TIMES, accumulate=False, variant=0):
-    _check_cuda(A.pos, A.crd, A.val, B, C)
+    """B may be a column slice of a wider row-major array (unit column stride); its row stride is passed on."""
+    _check_cuda(A.pos, A.crd, A.val, C)
+    if not B.is_cuda or B.dim() != 2 or B.stride(1) != 1:
+        raise ValueError("B must be a CUDA matrix with unit column stride")
     k = B.shape[1]
     if C is None:
         C = torch.empty((A.nrows, k), dtype=torch.float64, device=B.device)

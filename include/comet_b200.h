@@ -493,7 +493,8 @@ COMET_B200_EXPORT int32_t comet_b200_dev_spmv_f64_i64(int64_t nrows, int64_t nnz
    1 = entry stream whenever the shape allows it (K even, at most 256; worth asking for with
    narrow B and a power-law A, where it is several times faster than the panels),
    2 = row panels, 3 = the entry stream with the rows of B staged by TMA bulk copies
-   (cp.async.bulk completing on an mbarrier) instead of per-lane cp.async.  For the row panels the low bits are (panel width in columns) |
+   (cp.async.bulk completing on an mbarrier) instead of per-lane cp.async; with bit 26 set as well, one
+   cp.async.bulk.tensor ... tile::gather4 copy per stage of four rows (a tensor map of B is built per call).  For the row panels the low bits are (panel width in columns) |
    (lanes per row << 16): the number of B columns handled per pass over A and the lane-group
    size, for tuning. */
 COMET_B200_EXPORT int32_t comet_b200_dev_spmm_f64_i64(int64_t nrows, int64_t ncols, int64_t nnz,

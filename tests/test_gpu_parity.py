@@ -109,11 +109,12 @@ def _gappy(n=6000, seed=5):
 
 @pytest.mark.parametrize("k", [128, 64, 96, 16, 2, 256])
 @pytest.mark.parametrize("make", [_gappy, _skewed])
-@pytest.mark.parametrize("family", [1, 3])
+@pytest.mark.parametrize("family", [1, 3, 7])
 def test_spmm_entry_stream_path(make, k, family):
-    """The entry-stream kernels (asked for by bits 24-25 of the variant: 1 = rows of B staged with cp.async,
-    the default from 64 columns on; 3 = staged by TMA bulk copies completing on mbarriers): rows cut by
-    block boundaries, empty rows at every position, both store modes."""
+    """The entry-stream kernels (asked for by bits 24-26 of the variant: 1 = rows of B staged with cp.async,
+    the default from 64 columns on; 3 = staged by TMA bulk copies completing on mbarriers; 7 = staged by one
+    tile::gather4 tensor copy per four rows): rows cut by block boundaries, empty rows at every position, both
+    store modes."""
     A = make()
     B = datasets.dense_uniform((A.ncols, k), 3)
     C0 = datasets.dense_uniform((A.nrows, k), 4)
@@ -126,10 +127,21 @@ def test_spmm_entry_stream_path(make, k, family):
     _close(C.cpu().numpy(), oracle.spmm(_orc(A), B, C0), scale)
 
 
-def test_spmm_tma_staging_on_a_power_law_matrix():
+@pytest.mark.parametrize("family", [3, 7])
+def test_spmm_tma_staging_on_a_power_law_matrix(family):
     A, B = datasets.config_spmm(scale=14, edge_factor=16, k=128)
     dA, dB = dev.to_device(A), torch.from_numpy(B).cuda()
-    C = dev.spmm(dA, dB, variant=3 << 24)
+    C = dev.spmm(dA, dB, variant=family << 24)
+    _close(C.cpu().numpy(), oracle.spmm(_orc(A), B), oracle.spmm(_abs(A), np.abs(B)))
+
+
+def test_spmm_gather4_staging_with_a_padded_leading_dimension():
+    """B is a view of a wider array: the tensor map's row stride is the leading dimension, not K."""
+    A = _skewed(3000, seed=12)
+    wide = datasets.dense_uniform((A.ncols, 80), 5)
+    dwide = torch.from_numpy(wide).cuda()
+    C = dev.spmm(dev.to_device(A), dwide[:, :64], variant=7 << 24)
+    B = np.ascontiguousarray(wide[:, :64])
     _close(C.cpu().numpy(), oracle.spmm(_orc(A), B), oracle.spmm(_abs(A), np.abs(B)))
 
 
