@@ -525,7 +525,10 @@ COMET_B200_EXPORT int32_t comet_b200_dev_spmm_noalloc_f64_i64(
     const int64_t *crd, const double *val, const double *b, int64_t ldb, double *c, int64_t ldc,
     int32_t semiring, int32_t accumulate, void *stream);
 
-/* c[m, ncols] (+)= a[m, rows(B)] * B for the nstored rows B holds (row_ids as above). */
+/* c[m, ncols] (+)= a[m, rows(B)] * B for the nstored rows B holds (row_ids as above).  With 32 or more rows
+   of a and B in plain CSR (row_ids null) the product is formed transposed, C^T = B^T A^T, through the SpMM
+   kernels (B is transposed on the device first; temporaries of the size of a, c and B come from the stream's
+   memory pool); otherwise one f64 atomic per product and row of a. */
 COMET_B200_EXPORT int32_t comet_b200_dev_dense_times_sparse_f64_i64(
     int64_t m, int64_t ncols, int64_t nstored, int64_t nnz, const int64_t *row_ids, const int64_t *pos,
     const int64_t *crd, const double *val, const double *a, int64_t lda, double *c, int64_t ldc,

@@ -501,6 +501,25 @@ def test_dense_times_sparse(fmt, tmp_path):
                           oracle.dense_times_sparse(x, B, semiring=oracle.PLUS_PAIR))
 
 
+@pytest.mark.parametrize("m", [32, 33, 130])
+def test_dense_times_sparse_many_rows(m, monkeypatch):
+    """From 32 rows of the dense operand on (B in CSR) the product is formed as C^T = B^T A^T by the SpMM
+    kernels; odd row counts are padded to an even width.  Held to the oracle, and to the atomics kernel."""
+    B = _skewed(3000, seed=41)
+    A = datasets.dense_uniform((m, B.nrows), 2)
+    C0 = datasets.dense_uniform((m, B.ncols), 3)
+    absB = _abs(B)
+    want = oracle.dense_times_sparse(A, _orc(B))
+    scale = oracle.dense_times_sparse(np.abs(A), absB, np.abs(C0))
+    got = api.dense_times_sparse(A, B)
+    _close(got, want, scale)
+    _close(api.dense_times_sparse(A, B, C0), oracle.dense_times_sparse(A, _orc(B), C0), scale)
+    assert np.array_equal(api.dense_times_sparse(A, B, semiring=api.PLUS_PAIR),
+                          oracle.dense_times_sparse(A, _orc(B), semiring=oracle.PLUS_PAIR))
+    monkeypatch.setenv("COMET_B200_DENSE_SPARSE_ATOMICS", "1")
+    _close(api.dense_times_sparse(A, B), got, scale)
+
+
 @pytest.mark.parametrize("fmt", ["CSR", "DCSR", "COO"])
 def test_elews_sparse_dense_to_dense(fmt, tmp_path):
     Am = _skewed(500, seed=41)
