@@ -356,8 +356,12 @@ static const int64_t LONG_B_ROW = 1024;
 
 static const int LONG_LIST = 1024;          // long rows of B remembered per pass over a row of A
 
-// Calls f(q, p) for every product of row r of A with B in this CTA's share: q runs over the entries
-// of row acrd[p] of B.  A team of `team` CTAs deals the entries p of the A row out over its warps.
+// Calls f(j, bv, av) for every product of row r of A with B in this CTA's share: j and bv are the column and
+// value of an entry of row acrd[p] of B (bv = 0 when bval is null), av = aval[p] (0 when aval is null).  A team
+// of `team` CTAs deals the entries of the A row out over its warps one by one.  The loads are arranged so that
+// no warp waits on a chain: 32 entries of a warp's share look up their rows of B lane-parallel (acrd, then
+// bpos, once per batch), the first 32 entries of the next row of B are fetched before the current row is
+// worked on, and longer rows are walked two vectors per step with both loads issued first.
 // Short rows of B are walked by one warp; long ones are remembered in s_long and then walked by the
 // whole CTA.  s_ctl: [0] entries in s_long, [1] set when the list was too small (then the share is
 // scanned again for long rows).  All threads of the CTA must call this.
@@ -366,7 +370,9 @@ __device__ __forceinline__ void for_each_product(int64_t r, unsigned part, unsig
                                                  const int64_t *__restrict__ apos,
                                                  const int64_t *__restrict__ acrd,
                                                  const double *__restrict__ aval,
-                                                 const int64_t *__restrict__ bpos, int *s_long,
+                                                 const int64_t *__restrict__ bpos,
+                                                 const int32_t *__restrict__ bcrd,
+                                                 const double *__restrict__ bval, int *s_long,
                                                  unsigned *s_ctl, F f)
 {
     constexpr int NW = BM_THREADS / 32;
@@ -374,47 +380,83 @@ __device__ __forceinline__ void for_each_product(int64_t r, unsigned part, unsig
     const int64_t as = apos[r], ae = apos[r + 1];
     if (threadIdx.x == 0) { s_ctl[0] = 0; s_ctl[1] = 0; }
     __syncthreads();
-    // the row of B of the next entry is looked up while the current one is walked
+    // this warp's entries of the A row: first, first + stride, ... (dealt one by one, so that the warps of a
+    // team share a row of any length evenly); 32 of them at a time are looked up lane-parallel
     const int64_t stride = (int64_t)team * NW;
-    int64_t p = as + (int64_t)part * NW + warp;
-    int64_t s = 0, e = 0;
-    double av = 0.0;
-    if (p < ae) {
-        const int64_t k = acrd[p];
-        s = bpos[k];
-        e = bpos[k + 1];
-        if (aval) av = aval[p];
-    }
-    while (p < ae) {
-        const int64_t pn = p + stride;
-        int64_t sn = 0, en = 0;
-        double avn = 0.0;
-        if (pn < ae) {
-            const int64_t kn = acrd[pn];
-            sn = bpos[kn];
-            en = bpos[kn + 1];
-            if (aval) avn = aval[pn];
-        }
-        if (e - s > LONG_B_ROW) {
-            if (lane == 0) {
+    const int64_t first = as + (int64_t)part * NW + warp;
+    for (int64_t p0 = first; p0 < ae; p0 += 32 * stride) {
+        const int64_t p = p0 + lane * stride;
+        int64_t s_l = 0;
+        int n_l = 0;                     // entries of this lane's row of B; 0 for lanes past the A row and long rows
+        double av_l = 0.0;
+        if (p < ae) {
+            const int64_t k = acrd[p];
+            s_l = bpos[k];
+            const int64_t len = bpos[k + 1] - s_l;
+            if (aval) av_l = aval[p];
+            if (len > LONG_B_ROW) {
                 const unsigned at = atomicAdd(&s_ctl[0], 1u);
                 if (at < (unsigned)LONG_LIST) s_long[at] = (int)(p - as);
                 else s_ctl[1] = 1;
+            } else {
+                n_l = (int)len;
             }
-        } else {
-            for (int64_t q = s + lane; q < e; q += 32) f(q, av);
         }
-        p = pn; s = sn; e = en; av = avn;
+        const int64_t left = (ae - p0 + stride - 1) / stride;      // entries of the sequence from p0 on
+        const int n = left < 32 ? (int)left : 32;
+        // row t of the batch: start, length, value of A, and the first vector of its entries
+        int64_t s0 = __shfl_sync(0xffffffffu, (long long)s_l, 0);
+        int n0 = __shfl_sync(0xffffffffu, n_l, 0);
+        double a0 = shfl_f64(av_l, 0, 32);
+        int32_t j0 = 0;
+        double v0 = 0.0;
+        if (lane < n0) {
+            j0 = bcrd[s0 + lane];
+            if (bval) v0 = bval[s0 + lane];
+        }
+        for (int t = 0; t < n; t++) {
+            const int tn = (t + 1) & 31;                 // past the batch: lane 0 again, never used
+            const int64_t s1 = __shfl_sync(0xffffffffu, (long long)s_l, tn);
+            int n1 = __shfl_sync(0xffffffffu, n_l, tn);
+            if (t + 1 >= n) n1 = 0;
+            const double a1 = shfl_f64(av_l, tn, 32);
+            int32_t j1 = 0;
+            double v1 = 0.0;
+            if (lane < n1) {
+                j1 = bcrd[s1 + lane];
+                if (bval) v1 = bval[s1 + lane];
+            }
+            if (lane < n0) f(j0, v0, a0);
+            for (int64_t q = s0 + 32 + lane; q < s0 + n0; q += 64) {
+                const bool two = q + 32 < s0 + n0;
+                const int32_t ja = bcrd[q];
+                const int32_t jb = two ? bcrd[q + 32] : 0;
+                const double va = bval ? bval[q] : 0.0;
+                const double vb = (bval && two) ? bval[q + 32] : 0.0;
+                f(ja, va, a0);
+                if (two) f(jb, vb, a0);
+            }
+            s0 = s1; n0 = n1; a0 = a1; j0 = j1; v0 = v1;
+        }
     }
     __syncthreads();
+    auto whole_cta = [&](int64_t sl, int64_t el, double avl) {
+        for (int64_t q = sl + threadIdx.x; q < el; q += 2 * BM_THREADS) {
+            const bool two = q + BM_THREADS < el;
+            const int32_t ja = bcrd[q];
+            const int32_t jb = two ? bcrd[q + BM_THREADS] : 0;
+            const double va = bval ? bval[q] : 0.0;
+            const double vb = (bval && two) ? bval[q + BM_THREADS] : 0.0;
+            f(ja, va, avl);
+            if (two) f(jb, vb, avl);
+        }
+    };
     if (!s_ctl[1]) {
         const unsigned n = s_ctl[0];
         for (unsigned i = 0; i < n; i++) {
             const int64_t pl = as + s_long[i];
             const int64_t k = acrd[pl];
-            const int64_t el = bpos[k + 1];
-            const double avl = aval ? aval[pl] : 0.0;
-            for (int64_t q = bpos[k] + threadIdx.x; q < el; q += BM_THREADS) f(q, avl);
+            whole_cta(bpos[k], bpos[k + 1], aval ? aval[pl] : 0.0);
         }
     } else {
         for (int64_t p0 = as + (int64_t)part * NW; p0 < ae; p0 += stride)
@@ -422,8 +464,7 @@ __device__ __forceinline__ void for_each_product(int64_t r, unsigned part, unsig
                 const int64_t k = acrd[pl];
                 const int64_t sl = bpos[k], el = bpos[k + 1];
                 if (el - sl <= LONG_B_ROW) continue;
-                const double avl = aval ? aval[pl] : 0.0;
-                for (int64_t q = sl + threadIdx.x; q < el; q += BM_THREADS) f(q, avl);
+                whole_cta(sl, el, aval ? aval[pl] : 0.0);
             }
     }
 }
@@ -438,8 +479,7 @@ __device__ __forceinline__ void mark_products(uint32_t *bm, int64_t r, const int
 {
     int64_t ms = 0, me = 0;
     if (mpos) { ms = mpos[r]; me = mpos[r + 1]; }
-    for_each_product(r, 0u, 1u, apos, acrd, nullptr, bpos, s_long, s_ctl, [&](int64_t q, double) {
-        int32_t j = bcrd[q];
+    for_each_product(r, 0u, 1u, apos, acrd, nullptr, bpos, bcrd, nullptr, s_long, s_ctl, [&](int32_t j, double, double) {
         if (mpos && !in_mask(mcrd, ms, me, j)) return;
         atomicOr(&bm[j >> 5], 1u << (j & 31));          // testing the bit first was measured slower (6.4 vs 5.2 ms)
     });
@@ -611,7 +651,7 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
         const int64_t r = list[it];
         if (bm_store) {
             const uint32_t *keep = bm_store + (size_t)it * words;
-            for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = keep[w];
+            for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = __ldcs(keep + w);     // read once per member
             __syncthreads();
         } else {
             for (int w = threadIdx.x; w < words; w += BM_THREADS) bm[w] = 0;
@@ -646,14 +686,13 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
         __syncthreads();
         // accumulate every product at the rank of its column
         double *crow = cval + base;
-        for_each_product(r, part, team, apos, acrd, aval, bpos, s_long, s_ctl, [&](int64_t q, double av) {
-            int32_t j = bcrd[q];
+        for_each_product(r, part, team, apos, acrd, aval, bpos, bcrd, bval, s_long, s_ctl, [&](int32_t j, double bv, double av) {
             uint32_t word = bm[j >> 5];
             uint32_t bit = 1u << (j & 31);
             if (!(word & bit)) return;          // filtered out by the mask
             unsigned rank = pre[j >> 5] + __popc(word & (bit - 1u));
-            if (PLUS_TIMES) atomicAdd(crow + rank, av * bval[q]);
-            else sr_fold(semi, crow + rank, sr_combine(semi, av, bval[q]));
+            if (PLUS_TIMES) atomicAdd(crow + rank, av * bv);
+            else sr_fold(semi, crow + rank, sr_combine(semi, av, bv));
         });
         __syncthreads();
     }
