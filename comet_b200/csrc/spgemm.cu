@@ -354,6 +354,7 @@ __device__ __forceinline__ unsigned block_sum_u32(unsigned v, unsigned *s_warp)
 // fifteen wait at the next barrier was the largest stall of both passes.
 static const int64_t LONG_B_ROW = 1024;
 
+static const unsigned BM_DENSE_ROW = 96;    // bits in 32 consecutive bitmap words from which crd is written word by word
 static const int LONG_LIST = 1024;          // long rows of B remembered per pass over a row of A
 
 // Calls f(j, bv, av) for every product of row r of A with B in this CTA's share: j and bv are the column and
@@ -632,7 +633,7 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
     uint32_t *bm = SMEM ? s_dyn : gbm + (size_t)blockIdx.x * 2 * words;
     uint32_t *pre = bm + words;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per = (words + BM_THREADS - 1) / BM_THREADS;   // words per thread, contiguous
+    constexpr int NW = BM_THREADS / 32;
     for (unsigned iter = blockIdx.x;; iter += gridDim.x) {
         // one row per CTA, or (with an item list) the next member of a team
         unsigned it = iter, part = 0, team = 1;
@@ -659,26 +660,62 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
             mark_products(bm, r, apos, acrd, bpos, bcrd, mpos, mcrd, s_long, s_ctl);
             __syncthreads();
         }
-        // exclusive prefix popcount per word
-        const int w0 = threadIdx.x * per, w1 = min(w0 + per, words);
+        // Exclusive prefix popcount per word, and the row's coordinates.  A warp owns a run of whole rows of 32
+        // consecutive words; lane l of the warp holds word l of the current row, so every shared-memory access
+        // below is conflict-free and the prefix inside a row is a warp scan.
+        const int nrow32 = (words + 31) >> 5;
+        const int rows_per_warp = (nrow32 + NW - 1) / NW;
+        const int i0 = warp * rows_per_warp, i1 = min(i0 + rows_per_warp, nrow32);
         unsigned mine = 0;
-        for (int w = w0; w < w1; w++) mine += __popc(bm[w]);
-        unsigned run = block_excl_scan_u32(mine, s_scan);
+        for (int i = i0; i < i1; i++) {
+            const int w = i * 32 + lane;
+            if (w < words) mine += __popc(bm[w]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+        if (lane == 0) s_scan[warp] = mine;
+        __syncthreads();
+        unsigned run = 0;
+        for (int w2 = 0; w2 < warp; w2++) run += s_scan[w2];
         const int64_t base = cpos[r];
         const int64_t rown = cpos[r + 1] - base;
-        const bool my_crd = (threadIdx.x % team) == part;     // the members share the writing of crd
-        for (int w = w0; w < w1; w++) {
-            uint32_t v = bm[w];
-            pre[w] = run;
-            if (my_crd) {
-                while (v) {
-                    int b = __ffs(v) - 1;
-                    v &= v - 1;
-                    __stcs((long long *)ccrd + base + run, (long long)w * 32 + b);   // written once, not read here again
-                    run++;
+        for (int i = i0; i < i1; i++) {
+            const int w = i * 32 + lane;
+            uint32_t v = w < words ? bm[w] : 0u;
+            const unsigned c = __popc(v);
+            unsigned incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const unsigned excl = run + incl - c;
+            if (w < words) pre[w] = excl;
+            const unsigned rowtotal = __shfl_sync(0xffffffffu, incl, 31);
+            run += rowtotal;
+            // the members of a team share the writing of crd by rows of 32 words
+            if (rowtotal == 0 || (team > 1 && (unsigned)i % team != part)) continue;
+            if (rowtotal >= BM_DENSE_ROW) {
+                // many bits per word: one word at a time, lane b writes column 32 w + b at its rank, so a
+                // store instruction covers consecutive addresses
+                unsigned nz = __ballot_sync(0xffffffffu, v != 0u);
+                while (nz) {
+                    const int l = __ffs(nz) - 1;
+                    nz &= nz - 1;
+                    const uint32_t wv = __shfl_sync(0xffffffffu, v, l);
+                    const unsigned wp = __shfl_sync(0xffffffffu, excl, l);
+                    if ((wv >> lane) & 1u)
+                        __stcs((long long *)ccrd + base + wp + __popc(wv & ((1u << lane) - 1u)),
+                               (long long)(i * 32 + l) * 32 + lane);
                 }
             } else {
-                run += __popc(v);
+                unsigned at = excl;
+                while (v) {
+                    const int b = __ffs(v) - 1;
+                    v &= v - 1;
+                    __stcs((long long *)ccrd + base + at, (long long)w * 32 + b);   // written once, not read here again
+                    at++;
+                }
             }
         }
         if (team == 1)
