@@ -698,15 +698,15 @@ bitmap_numeric_kernel(unsigned nlist, const int32_t *__restrict__ list, int word
             if (rowtotal >= BM_DENSE_ROW) {
                 // many bits per word: one word at a time, lane b writes column 32 w + b at its rank, so a
                 // store instruction covers consecutive addresses
-                unsigned nz = __ballot_sync(0xffffffffu, v != 0u);
-                while (nz) {
-                    const int l = __ffs(nz) - 1;
-                    nz &= nz - 1;
+                // (all 32 words in a fixed-trip loop: the shuffles of different words do not depend on each
+                // other, so they overlap; a loop over the non-empty words only ran one word per shuffle latency)
+                long long *out = (long long *)ccrd + base;
+                const unsigned below = (1u << lane) - 1u;
+#pragma unroll 8
+                for (int l = 0; l < 32; l++) {
                     const uint32_t wv = __shfl_sync(0xffffffffu, v, l);
                     const unsigned wp = __shfl_sync(0xffffffffu, excl, l);
-                    if ((wv >> lane) & 1u)
-                        __stcs((long long *)ccrd + base + wp + __popc(wv & ((1u << lane) - 1u)),
-                               (long long)(i * 32 + l) * 32 + lane);
+                    if ((wv >> lane) & 1u) __stcs(out + wp + __popc(wv & below), (long long)(i * 32 + l) * 32 + lane);
                 }
             } else {
                 unsigned at = excl;
