@@ -354,7 +354,7 @@ __device__ __forceinline__ unsigned block_sum_u32(unsigned v, unsigned *s_warp)
 // fifteen wait at the next barrier was the largest stall of both passes.
 static const int64_t LONG_B_ROW = 1024;
 
-static const unsigned BM_DENSE_ROW = 96;    // bits in 32 consecutive bitmap words from which crd is written word by word
+static const unsigned BM_DENSE_ROW = 512;   // bits in 32 consecutive bitmap words from which crd is written word by word (measured: 96 / 192 / 320 / 512 / 768 / never = 22.9 / 21.8 / 21.5 / 21.45 / 21.65 / 21.7 ms numeric at config 4)
 static const int LONG_LIST = 1024;          // long rows of B remembered per pass over a row of A
 
 // Calls f(j, bv, av) for every product of row r of A with B in this CTA's share: j and bv are the column and
