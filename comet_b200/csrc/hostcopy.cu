@@ -119,7 +119,6 @@ class Pool {
         return f ? 1 : 0;
     }
     void fail_flag() { failed_ = true; }
-    int device() const { return device_; }
 
   private:
     void work()

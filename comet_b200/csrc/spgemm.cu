@@ -486,23 +486,6 @@ __device__ __forceinline__ void mark_products(uint32_t *bm, int64_t r, const int
     });
 }
 
-// exclusive prefix sum of one value per thread over the CTA (s_warp: one slot per warp)
-__device__ __forceinline__ unsigned block_excl_scan_u32(unsigned v, unsigned *s_warp)
-{
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    unsigned incl = v;
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += t;
-    }
-    __syncthreads();                    // s_warp may still be read by the previous use
-    if (lane == 31) s_warp[warp] = incl;
-    __syncthreads();
-    unsigned before = 0;
-    for (int w = 0; w < warp; w++) before += s_warp[w];
-    return before + incl - v;
-}
-
 template <bool SMEM>
 __global__ void __launch_bounds__(BM_THREADS)
 bitmap_symbolic_kernel(unsigned nlist, const int32_t *__restrict__ list, int words,
