@@ -833,14 +833,17 @@ class Env:
 def rebalance(w, env, args):
     """Cuts the rows into blocks of equal MEASURED work.  The first cut balances a model weight per row;
     each round then times one warm-up pass per rank, charges every row of a block with that block's
-    measured time per unit of weight, and cuts again.  Part of set-up, like the first split."""
+    measured time per unit of weight, and cuts again; the cut whose slowest rank was fastest is the one
+    kept.  Part of set-up, like the first split.  Returns the per-rank times of every round and the
+    index of the round whose cut was kept."""
     torch, dist, dev, sharding = env.torch, env.dist, env.dev, env.sharding
     weights = np.asarray(w.weights, dtype=np.float64)
     bounds = sharding.row_blocks(w.A.a2pos, env.world, weights=weights)
     w.place(bounds, torch, dev, sharding)
     history = []
     if env.world == 1:
-        return history
+        return history, 0
+    best = None                                            # (slowest rank's time, round, bounds)
     for _ in range(args.rebalance_rounds + 1):
         w.run_steps(2, dev, sharding, with_collective=False)
         torch.cuda.synchronize()
@@ -856,6 +859,8 @@ def rebalance(w, env, args):
         dist.all_gather(ts, t)
         times = np.array([float(x.item()) for x in ts])
         history.append([round(float(x), 4) for x in times])
+        if best is None or times.max() < best[0]:
+            best = (float(times.max()), len(history) - 1, np.array(bounds).copy())
         if len(history) > args.rebalance_rounds or times.max() <= 1.04 * times.min():
             break
         cum = np.concatenate([[0.0], np.cumsum(weights)])
@@ -869,7 +874,9 @@ def rebalance(w, env, args):
         weights /= weights.sum() / 1e9
         bounds = sharding.row_blocks(w.A.a2pos, env.world, weights=weights)
         w.place(bounds, torch, dev, sharding)
-    return history
+    if best[1] != len(history) - 1:                        # (the times are all-gathered: every rank decides alike)
+        w.place(best[2], torch, dev, sharding)
+    return history, best[1]
 
 
 def measure(w, args, env, headline):
@@ -883,7 +890,7 @@ def measure(w, args, env, headline):
         torch.cuda.synchronize()
 
     w.build()
-    history = rebalance(w, env, args)
+    history, kept_round = rebalance(w, env, args)
     w.run_steps(args.warmup, dev, sharding)
     w.run_steps(args.steps, dev, sharding)      # also builds anything cached per step count
     barrier()
@@ -986,6 +993,7 @@ def measure(w, args, env, headline):
     }
     if world > 1:
         res["rebalance_per_rank_ms"] = history
+        res["rebalance_kept_round"] = kept_round
         res["row_bounds"] = [int(b) for b in kernel_bounds]
         if e2e_bounds is not None:
             res["e2e_row_bounds"] = [int(b) for b in e2e_bounds]
@@ -1126,7 +1134,7 @@ def main():
             "clocks": clocks,
         }
         for key in ("e2e", "e2e_pageable", "gpu_launches", "roofline", "per_rank_kernel_ms", "parity_checked",
-                    "cpu_baseline", "rebalance_per_rank_ms", "row_bounds", "e2e_row_bounds", "e2e_row_bounds_note",
+                    "cpu_baseline", "rebalance_per_rank_ms", "rebalance_kept_round", "row_bounds", "e2e_row_bounds", "e2e_row_bounds_note",
                     "probes_per_s", "nnz_c", "latency"):
             if key in head:
                 line[key] = head[key]
