@@ -848,7 +848,7 @@ def rebalance(w, env, args):
         w.run_steps(2, dev, sharding, with_collective=False)
         torch.cuda.synchronize()
         dist.barrier()
-        reps = 3 if w.name in ("spgemm", "triangles") else 10      # short kernels need more repetitions for a steady figure
+        reps = 3 if w.name in ("spgemm", "triangles") else 30      # short kernels need more repetitions for a steady figure
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         w.run_steps(reps, dev, sharding, with_collective=False)
@@ -1063,7 +1063,7 @@ def main():
     ap.add_argument("--k", type=int, default=0, help="override the dense width")
     ap.add_argument("--variant", type=int, default=0, help="SpMM kernel family / panel shape (tuning)")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--rebalance-rounds", type=int, default=3)
+    ap.add_argument("--rebalance-rounds", type=int, default=5)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (no end-to-end leg, no CPU leg): for profiler runs")
